@@ -52,7 +52,7 @@ class CacheStorage:
         for c, r in kv_requests.items():
             shape = (pages_per_group[group_index[c]], r.num_kv_heads, page_size)
             self.kv[c] = (torch.zeros(shape + (r.head_dim,), dtype=dtype, device=device),
-                          torch.zeros(shape + (r.value_dim,), dtype=dtype, device=device))
+                          torch.zeros(shape + (r.value_dim,), dtype=dtype, device=device) if r.values else None)
         for c, r in state_requests.items():
             self.state[c] = torch.zeros((num_state_slots, *r.shape), dtype=r.dtype, device=device)
 
@@ -72,5 +72,5 @@ class CacheStorage:
             t.index_fill_(0, idx, 0)
 
     def bytes_held(self) -> int:
-        n = sum(k.numel() * k.element_size() + v.numel() * v.element_size() for k, v in self.kv.values())
+        n = sum(t.numel() * t.element_size() for kv in self.kv.values() for t in kv if t is not None)
         return n + sum(t.numel() * t.element_size() for t in self.state.values())

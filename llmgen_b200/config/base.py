@@ -120,7 +120,7 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def architecture_name(data: dict, where: str = "config.json") -> str:
-    """The registry key of a config dict: `architectures[0]`, else `model_type`.
+    """The registry key of a config dict: `architectures[0]`, else `model_type`, else `architecture`.
 
     The reference keys its registry by GGUF `general.architecture`
     (src/models/factory.zig:68-71); for a config.json folder the same role is played by
@@ -129,7 +129,8 @@ def architecture_name(data: dict, where: str = "config.json") -> str:
     archs = data.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = data.get("model_type")
-    if isinstance(mt, str) and mt:
-        return mt
-    raise ConfigError(f"{where}: neither 'architectures' nor 'model_type' names the model")
+    for key in ("model_type", "architecture"):
+        name = data.get(key)
+        if isinstance(name, str) and name:
+            return name
+    raise ConfigError(f"{where}: none of 'architectures', 'model_type' and 'architecture' names the model")

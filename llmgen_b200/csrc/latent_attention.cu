@@ -1,0 +1,500 @@
+// Attention whose keys and values are expanded from one cached latent vector per token (multi-head latent
+// attention).  Per token the cache holds  z = [c | kr]:  c = rmsnorm(c~) * gain  [rank]  and one rotated key part
+// kr [rot] shared by all heads; head h's key is [Wuk_h c | kr] and its value Wuv_h c.  Instead of expanding the
+// keys of the whole context, the query is taken into the latent space and the output out of it:
+//
+//   score_ij = (qn_i . Wuk_h c_j + qr_i . kr_j) * scale = ([Wuk_h^T qn_i | qr_i] . z_j) * scale
+//   o_i      = Wuv_h (sum_j p_ij c_j)
+//
+// so the attention itself is one shared "kv head" of width rank + rot whose values are the first `rank` entries of
+// the same cached vector.  Four kernels:
+//
+//   latent_prep      per token: cq = rmsnorm(dq~) * gain (the query's latent, for the product that follows);
+//                    c and the rotated kr written to the token's place in the paged cache
+//   latent_absorb    qa[t, h] = [Wuk_h^T qn | rotate(qr)]                      float32 [tokens, heads, rank + rot]
+//   latent_attention causal softmax attention of qa over the cached z; float32 scores, weights and sums
+//                    (+ latent_reduce for key parts, flash-decoding)            float32 [tokens, heads, rank]
+//   latent_expand    out[t, h] = (Wuv_h oa[t, h]) * sigmoid(g[t, h])           storage dtype [tokens, heads * vdim]
+//
+// Rotation: pairs (2i, 2i + 1) ("interleaved") or (i, i + rot/2) ("half"), by the angle whose cos / sin the tables
+// hold per position.  Positions, angles, norms, scores, softmax and all sums are float32; the cache and the
+// matrices have the storage dtype.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+__device__ __forceinline__ void rotate_into(float* dst, const float* src, int rot, int pairing, const float* cs, const float* sn,
+                                            int i) {
+    // pair i of rot / 2
+    const int a = pairing == LLMK_PAIR_INTERLEAVED ? 2 * i : i;
+    const int b = pairing == LLMK_PAIR_INTERLEAVED ? 2 * i + 1 : i + rot / 2;
+    const float u = src[a], v = src[b], c = cs[i], s = sn[i];
+    dst[a] = u * c - v * s;
+    dst[b] = v * c + u * s;
+}
+
+// ---------------------------------------------------------------------------------------------- prep
+// One block per token.  `dq` [q_rank] and `dkv` [rank + rot] are read from the packed projection row.
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ packed, long long ld, int dq_off, int dkv_off, int q_rank, int rank, int rot,
+                                   const float* __restrict__ q_gain, const float* __restrict__ kv_gain, float eps,
+                                   T* __restrict__ cq_out, T* __restrict__ cache, const int* __restrict__ positions,
+                                   const int* __restrict__ slots, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                   int pairing) {
+    extern __shared__ float sm[];   // rot floats in, rot floats out, 33 scratch
+    float* kr_in = sm;
+    float* kr_out = sm + rot;
+    float* scratch = sm + 2 * rot;
+    const size_t t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* row = packed + t * ld;
+    if (cq_out && q_rank > 0) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+            const float v = to_float(row[dq_off + i]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float rinv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+            cq_out[t * q_rank + i] = from_float<T>(to_float(row[dq_off + i]) * rinv * q_gain[i]);
+    }
+    const int slot = slots ? slots[t] : -1;
+    if (slot < 0 || !cache) return;      // a row that belongs to no sequence, or a pass that stores nothing
+    T* z = cache + (size_t)slot * (rank + rot);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+        const float v = to_float(row[dkv_off + i]);
+        ss += v * v;
+    }
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) kr_in[i] = to_float(row[dkv_off + rank + i]);
+    ss = block_sum(ss, scratch);         // also orders kr_in
+    const float rinv = 1.0f / sqrtf(ss / (float)rank + eps);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) z[i] = from_float<T>(to_float(row[dkv_off + i]) * rinv * kv_gain[i]);
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < rot / 2; i += blockDim.x)
+        rotate_into(kr_out, kr_in, rot, pairing, cos_t + (size_t)pos * (rot / 2), sin_t + (size_t)pos * (rot / 2), i);
+    __syncthreads();
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) z[rank + i] = from_float<T>(kr_out[i]);
+}
+
+LLMK_EXPORT int llmk_latent_prep(const void* packed, long long ld, int dq_off, int dkv_off, int q_rank, int rank, int rot,
+                                 const float* q_gain, const float* kv_gain, float eps, void* cq_out, void* cache,
+                                 const int* positions, const int* slots, const float* cos_t, const float* sin_t, int pairing,
+                                 int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (rank <= 0 || rot < 0 || rot % 2 != 0) LLMK_FAIL("latent_prep: bad sizes (rank %d, rot %d)", rank, rot);
+    if (pairing != LLMK_PAIR_INTERLEAVED && pairing != LLMK_PAIR_HALF_SPLIT) LLMK_FAIL("latent_prep: unknown rotary pairing %d", pairing);
+    const size_t smem = ((size_t)2 * rot + 33) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(latent_prep_kernel<float>, dim3(n_tokens), dim3(128), smem, s, true, (const float*)packed, ld, dq_off, dkv_off,
+                        q_rank, rank, rot, q_gain, kv_gain, eps, (float*)cq_out, (float*)cache, positions, slots, cos_t, sin_t, pairing);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(latent_prep_kernel<bf16>, dim3(n_tokens), dim3(128), smem, s, true, (const bf16*)packed, ld, dq_off, dkv_off,
+                        q_rank, rank, rot, q_gain, kv_gain, eps, (bf16*)cq_out, (bf16*)cache, positions, slots, cos_t, sin_t, pairing);
+    else
+        LLMK_FAIL("latent_prep: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("latent_prep", e);
+    return LLMK_OK;
+}
+
+// -------------------------------------------------------------------------------------------- absorb
+// Block (tile of TT tokens, head).  q [tokens, heads * (dim + rot)] of T; wuk [heads * dim, rank] of T (as stored:
+// row h * dim + d is key dimension d of head h); qa float32 [tokens, heads, rank + rot].
+constexpr int LT_TT = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) latent_absorb_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ wuk,
+                                                            float* __restrict__ qa, const int* __restrict__ positions,
+                                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                            int n_tokens, int heads, int dim, int rot, int rank, int pairing) {
+    extern __shared__ float sm[];   // [TT][dim] unrotated parts, [TT][rot] rotated parts in, [TT][rot] out
+    float* qn = sm;
+    float* qr = qn + LT_TT * dim;
+    float* qo = qr + LT_TT * rot;
+    const int t0 = blockIdx.x * LT_TT, h = blockIdx.y;
+    const int n = min(LT_TT, n_tokens - t0);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int hd = dim + rot;
+    for (int idx = threadIdx.x; idx < LT_TT * hd; idx += blockDim.x) {
+        const int i = idx / hd, d = idx % hd;
+        const float v = i < n ? to_float(q[(size_t)(t0 + i) * ldq + (size_t)h * hd + d]) : 0.f;
+        if (d < dim) qn[i * dim + d] = v; else qr[i * rot + d - dim] = v;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < LT_TT * (rot / 2); idx += blockDim.x) {
+        const int i = idx / (rot / 2), pr = idx % (rot / 2);
+        if (i < n) {
+            const int pos = positions[t0 + i];
+            rotate_into(qo + i * rot, qr + i * rot, rot, pairing, cos_t + (size_t)pos * (rot / 2), sin_t + (size_t)pos * (rot / 2), pr);
+        }
+    }
+    const int za = rank + rot;
+    const T* w = wuk + (size_t)h * dim * rank;
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+        float acc[LT_TT];
+#pragma unroll
+        for (int i = 0; i < LT_TT; ++i) acc[i] = 0.f;
+        for (int d = 0; d < dim; ++d) {
+            const float wv = to_float(w[(size_t)d * rank + r]);
+#pragma unroll
+            for (int i = 0; i < LT_TT; ++i) acc[i] = fmaf(qn[i * dim + d], wv, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < LT_TT; ++i)
+            if (i < n) qa[((size_t)(t0 + i) * heads + h) * za + r] = acc[i];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < LT_TT * rot; idx += blockDim.x) {
+        const int i = idx / rot, d = idx % rot;
+        if (i < n) qa[((size_t)(t0 + i) * heads + h) * za + rank + d] = qo[idx];
+    }
+}
+
+LLMK_EXPORT int llmk_latent_absorb(float* qa, const void* q, long long ldq, const void* wuk, const int* positions,
+                                   const float* cos_t, const float* sin_t, int n_tokens, int heads, int dim, int rot, int rank,
+                                   int pairing, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (heads <= 0 || heads > 65535 || dim < 0 || rot < 0 || rot % 2 != 0 || rank <= 0) LLMK_FAIL("latent_absorb: bad sizes");
+    if (pairing != LLMK_PAIR_INTERLEAVED && pairing != LLMK_PAIR_HALF_SPLIT) LLMK_FAIL("latent_absorb: unknown rotary pairing %d", pairing);
+    const size_t smem = (size_t)LT_TT * (dim + 2 * rot) * sizeof(float);
+    dim3 grid(ceil_div(n_tokens, LT_TT), heads);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_absorb_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, s, true, (const float*)q, ldq, (const float*)wuk, qa, positions,
+                        cos_t, sin_t, n_tokens, heads, dim, rot, rank, pairing);
+    } else if (dtype == LLMK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_absorb_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, s, true, (const bf16*)q, ldq, (const bf16*)wuk, qa, positions,
+                        cos_t, sin_t, n_tokens, heads, dim, rot, rank, pairing);
+    } else
+        LLMK_FAIL("latent_absorb: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("latent_absorb", e);
+    return LLMK_OK;
+}
+
+// ----------------------------------------------------------------------------------------- attention
+// One block per (tile of queries of one sequence, chunk of heads, key part): up to 16 rows = bq queries x gc
+// heads, two rows a warp; every tile of 32 cached vectors is read once for all rows of the block.  Sequence s owns
+// query rows [cu_q[s], cu_q[s+1]) and has ctx[s] keys after this step; query j of the portion sits at position
+// ctx - q_len + j and sees keys 0..position.  The step's own vectors were written to the cache before.
+constexpr int LT_WARPS = 8;
+constexpr int LT_ROWS = 16;
+constexpr int LT_KT = 32;
+
+struct LatentAttnParams {
+    const float* qa;           // [tokens, heads, za]
+    const void* cache;         // [pages, page_size, za]
+    float* out;                // [tokens, heads, rank]
+    const int* block_tables;
+    const int* ctx_len;
+    const int* cu_q;
+    const int* tile_seq;
+    const int* tile_q0;
+    float* part_o;
+    float* part_ml;
+    int max_blocks, heads, rank, za, page_size, num_parts, bq, gc, chunks;
+    float scale;
+};
+
+template <typename T, int RL>
+__global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentAttnParams p) {
+    extern __shared__ float smem[];
+    const int za = p.za, rank = p.rank;
+    float* Qs = smem;                       // [ROWS][za], pre-multiplied by scale
+    float* Zs = Qs + LT_ROWS * za;          // [KT][za + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = p.tile_seq[blockIdx.x];
+    if (s < 0) return;                      // padding of a tile list of fixed length
+    const int q0 = p.tile_q0[blockIdx.x];
+    const int chunk = blockIdx.y, part = blockIdx.z;
+    const int q_beg = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - q_beg;
+    const int ctx = p.ctx_len[s];
+    const int nq_tile = min(p.bq, q_len - q0);
+    const bool padding = ctx < q_len || nq_tile <= 0;
+    const int first_pos = ctx - q_len + q0;
+    int k_beg = 0, k_end = 0;
+    if (!padding) k_end = first_pos + nq_tile;
+    if (p.num_parts > 1) {
+        const int part_size = ceil_div(ceil_div(max(ctx, 1), p.num_parts), LT_KT) * LT_KT;
+        k_beg = max(k_beg, part * part_size);
+        k_end = min(k_end, (part + 1) * part_size);
+    }
+    const T* zc = static_cast<const T*>(p.cache);
+    const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+    const int rows = p.bq * p.gc;
+    for (int idx = threadIdx.x; idx < LT_ROWS * za; idx += blockDim.x) {
+        const int r = idx / za, d = idx % za;
+        const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
+        float v = 0.f;
+        if (r < rows && qi < nq_tile && hh < p.heads) v = p.qa[((size_t)(q_beg + q0 + qi) * p.heads + hh) * za + d] * p.scale;
+        Qs[idx] = v;
+    }
+    int r_of[2], qi_of[2], head_of[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        r_of[i] = warp + i * LT_WARPS;
+        qi_of[i] = r_of[i] / p.gc;
+        head_of[i] = chunk * p.gc + r_of[i] % p.gc;
+        valid[i] = r_of[i] < rows && qi_of[i] < nq_tile && head_of[i] < p.heads && !padding;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[2][RL];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < RL; ++j) acc[i][j] = 0.f;
+
+    for (int t0 = k_beg; t0 < k_end; t0 += LT_KT) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < LT_KT * za; idx += blockDim.x) {
+            const int key = idx / za, d = idx % za;
+            const int kpos = t0 + key;
+            float v = 0.f;
+            if (kpos < k_end) {
+                const int page = bt[kpos / p.page_size];
+                v = to_float(zc[((size_t)page * p.page_size + kpos % p.page_size) * za + d]);
+            }
+            Zs[key * (za + 1) + d] = v;
+        }
+        __syncthreads();
+        if (!valid[0] && !valid[1]) continue;
+        float sc[2] = {0.f, 0.f};
+        {
+            const float* kr = Zs + lane * (za + 1);
+            const float* qa = Qs + r_of[0] * za;
+            const float* qb = Qs + (valid[1] ? r_of[1] : r_of[0]) * za;
+            for (int d = 0; d < za; ++d) {
+                const float kv = kr[d];
+                sc[0] = fmaf(qa[d], kv, sc[0]);
+                sc[1] = fmaf(qb[d], kv, sc[1]);
+            }
+        }
+        const int kpos = t0 + lane;
+        float pr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int qpos = first_pos + qi_of[i];
+            const bool ok = valid[i] && kpos < k_end && kpos <= qpos;
+            const float sv = ok ? sc[i] : -INFINITY;
+            const float tmax = warp_max(sv);
+            const float m_new = fmaxf(m[i], tmax);
+            float corr = 1.f;
+            pr[i] = 0.f;
+            if (m_new > -INFINITY) {
+                corr = m[i] > -INFINITY ? expf(m[i] - m_new) : 0.f;
+                pr[i] = ok ? expf(sv - m_new) : 0.f;
+                m[i] = m_new;
+            }
+            l[i] = l[i] * corr + warp_sum(pr[i]);
+#pragma unroll
+            for (int j = 0; j < RL; ++j) acc[i][j] *= corr;
+        }
+        const int kmax = min(LT_KT, k_end - t0);
+        for (int k = 0; k < kmax; ++k) {
+            const float p0 = __shfl_sync(0xffffffffu, pr[0], k);
+            const float p1 = __shfl_sync(0xffffffffu, pr[1], k);
+            const float* vr = Zs + k * (za + 1);
+#pragma unroll
+            for (int j = 0; j < RL; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rank) {
+                    const float v = vr[d];
+                    acc[0][j] = fmaf(p0, v, acc[0][j]);
+                    acc[1][j] = fmaf(p1, v, acc[1][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const bool owned = r_of[i] < rows && qi_of[i] < max(nq_tile, 0) && head_of[i] < p.heads;
+        if (!owned) continue;
+        const size_t tok = (size_t)(q_beg + q0 + qi_of[i]);
+        if (p.num_parts > 1) {
+            const size_t row = (tok * p.heads + head_of[i]) * p.num_parts + part;
+#pragma unroll
+            for (int j = 0; j < RL; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rank) p.part_o[row * rank + d] = acc[i][j];
+            }
+            if (lane == 0) {
+                p.part_ml[row * 2] = m[i];
+                p.part_ml[row * 2 + 1] = l[i];
+            }
+        } else {
+            float* o = p.out + (tok * p.heads + head_of[i]) * rank;
+            const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < RL; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rank) o[d] = acc[i][j] * inv;
+            }
+        }
+    }
+}
+
+// One warp per (token, head): merge the key parts in part order.
+__global__ void latent_reduce_kernel(float* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     int n_rows, int rank, int num_parts) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
+    if (row >= n_rows) return;
+    const float* ml = part_ml + (size_t)row * num_parts * 2;
+    float M = -INFINITY;
+    for (int pt = 0; pt < num_parts; ++pt)
+        if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
+    float denom = 0.f;
+    for (int pt = 0; pt < num_parts; ++pt)
+        if (ml[2 * pt + 1] > 0.f) denom += expf(ml[2 * pt] - M) * ml[2 * pt + 1];
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+    float* o = out + (size_t)row * rank;
+    for (int d = lane; d < rank; d += 32) {
+        float v = 0.f;
+        for (int pt = 0; pt < num_parts; ++pt)
+            if (ml[2 * pt + 1] > 0.f) v += expf(ml[2 * pt] - M) * part_o[((size_t)row * num_parts + pt) * rank + d];
+        o[d] = v * inv;
+    }
+}
+
+template <typename T, int RL>
+static int launch_latent_attention(const LatentAttnParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<T, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LLMK_FAIL("latent_attention: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+    }
+    LLMK_CHECK_LAUNCH_RC("latent_attention", llmk_launch(latent_attention_kernel<T, RL>, grid, dim3(LT_WARPS * 32), smem, s, true, p));
+    return LLMK_OK;
+}
+
+template <typename T>
+static int dispatch_latent_attention(const LatentAttnParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+    const int rl = ceil_div(p.rank, 32);
+    if (rl <= 1) return launch_latent_attention<T, 1>(p, grid, smem, s);
+    if (rl <= 2) return launch_latent_attention<T, 2>(p, grid, smem, s);
+    if (rl <= 4) return launch_latent_attention<T, 4>(p, grid, smem, s);
+    if (rl <= 8) return launch_latent_attention<T, 8>(p, grid, smem, s);
+    return launch_latent_attention<T, 16>(p, grid, smem, s);
+}
+
+// Queries per tile for `heads` heads: rows = bq * gc <= 16.
+LLMK_EXPORT int llmk_latent_attention_tile_queries(int heads) {
+    if (heads <= 0) return 0;
+    const int gc = heads < LT_ROWS ? heads : LT_ROWS;
+    return LT_ROWS / gc;
+}
+
+LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* cache, const int* block_tables, int max_blocks,
+                                      const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                      int n_tokens, int heads, int rank, int rot, int page_size, float scale, int num_parts,
+                                      float* scratch, int dtype, void* stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
+    if (heads <= 0 || rank <= 0 || rank > 512 || rot < 0) LLMK_FAIL("latent_attention: bad sizes (heads %d, rank %d, rot %d)", heads, rank, rot);
+    if (page_size <= 0) LLMK_FAIL("latent_attention: page_size %d", page_size);
+    if (num_parts < 1 || num_parts > 65535 || (num_parts > 1 && !scratch)) LLMK_FAIL("latent_attention: bad split (%d parts)", num_parts);
+    LatentAttnParams p;
+    p.gc = heads < LT_ROWS ? heads : LT_ROWS;
+    p.bq = LT_ROWS / p.gc;
+    p.chunks = ceil_div(heads, p.gc);
+    p.qa = qa; p.cache = cache; p.out = out; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.max_blocks = max_blocks; p.heads = heads; p.rank = rank; p.za = rank + rot;
+    p.page_size = page_size; p.num_parts = num_parts; p.scale = scale;
+    p.part_o = scratch;
+    p.part_ml = num_parts > 1 ? scratch + (size_t)n_tokens * heads * num_parts * rank : nullptr;
+    const size_t smem = ((size_t)LT_ROWS * p.za + (size_t)LT_KT * (p.za + 1)) * sizeof(float);
+    if (smem > 220 * 1024) LLMK_FAIL("latent_attention: cached vectors of %d values do not fit shared memory", p.za);
+    dim3 grid(n_tiles, p.chunks, num_parts);
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    if (dtype == LLMK_F32)
+        rc = dispatch_latent_attention<float>(p, grid, smem, s);
+    else if (dtype == LLMK_BF16)
+        rc = dispatch_latent_attention<bf16>(p, grid, smem, s);
+    else
+        LLMK_FAIL("latent_attention: unknown dtype %d", dtype);
+    if (rc != LLMK_OK) return rc;
+    if (num_parts > 1) {
+        const int n_rows = n_tokens * heads;
+        const int warps = 4;
+        LLMK_CHECK_LAUNCH_RC("latent_reduce", llmk_launch(latent_reduce_kernel, dim3(ceil_div(n_rows, warps)), dim3(warps * 32), 0, s, true,
+                                                          out, (const float*)p.part_o, (const float*)p.part_ml, n_rows, rank, num_parts));
+    }
+    return LLMK_OK;
+}
+
+// -------------------------------------------------------------------------------------------- expand
+// Block (tile of TT tokens, head); a warp per output value j of the head: out[t, h * vdim + j] =
+// (wuv[h * vdim + j, :] . oa[t, h, :]) * sigmoid(g[t, h * vdim + j]).
+template <typename T>
+__global__ void __launch_bounds__(256) latent_expand_kernel(T* __restrict__ out, const float* __restrict__ oa, const T* __restrict__ wuv,
+                                                            const T* __restrict__ g, long long ldg, int n_tokens, int heads, int rank,
+                                                            int vdim) {
+    extern __shared__ float os[];   // [TT][rank]
+    const int t0 = blockIdx.x * LT_TT, h = blockIdx.y;
+    const int n = min(LT_TT, n_tokens - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < LT_TT * rank; idx += blockDim.x) {
+        const int i = idx / rank, r = idx % rank;
+        os[idx] = i < n ? oa[((size_t)(t0 + i) * heads + h) * rank + r] : 0.f;
+    }
+    __syncthreads();
+    for (int j = warp; j < vdim; j += nwarps) {
+        const T* w = wuv + ((size_t)h * vdim + j) * rank;
+        float acc[LT_TT];
+#pragma unroll
+        for (int i = 0; i < LT_TT; ++i) acc[i] = 0.f;
+        for (int r = lane; r < rank; r += 32) {
+            const float wv = to_float(w[r]);
+#pragma unroll
+            for (int i = 0; i < LT_TT; ++i) acc[i] = fmaf(os[i * rank + r], wv, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < LT_TT; ++i) acc[i] = warp_sum(acc[i]);
+        if (lane < n) {
+            float v = 0.f;
+#pragma unroll
+            for (int i = 0; i < LT_TT; ++i)
+                if (i == lane) v = acc[i];
+            const size_t col = (size_t)h * vdim + j;
+            float gate = 1.f;
+            if (g) gate = 1.0f / (1.0f + expf(-to_float(g[(size_t)(t0 + lane) * ldg + col])));
+            out[(size_t)(t0 + lane) * ((size_t)heads * vdim) + col] = from_float<T>(v * gate);
+        }
+    }
+}
+
+LLMK_EXPORT int llmk_latent_expand(void* out, const float* oa, const void* wuv, const void* g, long long ldg, int n_tokens, int heads,
+                                   int rank, int vdim, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (heads <= 0 || heads > 65535 || rank <= 0 || vdim <= 0) LLMK_FAIL("latent_expand: bad sizes");
+    const size_t smem = (size_t)LT_TT * rank * sizeof(float);
+    dim3 grid(ceil_div(n_tokens, LT_TT), heads);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_expand_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(latent_expand_kernel<float>, grid, dim3(256), smem, s, true, (float*)out, oa, (const float*)wuv, (const float*)g, ldg,
+                        n_tokens, heads, rank, vdim);
+    } else if (dtype == LLMK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_expand_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(latent_expand_kernel<bf16>, grid, dim3(256), smem, s, true, (bf16*)out, oa, (const bf16*)wuv, (const bf16*)g, ldg,
+                        n_tokens, heads, rank, vdim);
+    } else
+        LLMK_FAIL("latent_expand: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("latent_expand", e);
+    return LLMK_OK;
+}

@@ -1,0 +1,177 @@
+// Row-wise kernels of layers that normalise a sublayer's OUTPUT before it joins the residual stream
+// (x <- x + norm(sublayer(x))), and of the sublayers such layers are made of:
+//
+//   norm_add        resid[r, :] += rmsnorm(y[r, :]) * w, and a copy of the new residual row in the storage dtype
+//                   for the products that read the residual itself
+//   cast_rows       out = (T) in, float32 in
+//   act_rows        relu(x)^2, or the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L)
+//   gated_rmsnorm   out[r, :] = rmsnorm(o[r, :]) * w * sigmoid(g[r, :])   (or, without gains, o * sigmoid(g))
+//
+// Sums of squares, gains, the residual and the activations' arithmetic are float32 in both storage dtypes.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+// y is a [n, H] array of T (splits == 0), or `splits` float32 slices `split_stride` floats apart, added in slice order.
+template <typename T>
+__device__ __forceinline__ float load_sum(const void* y, size_t at, int splits, long long split_stride) {
+    if (splits == 0) return to_float(static_cast<const T*>(y)[at]);
+    const float* p = static_cast<const float*>(y) + at;
+    float acc = p[0];
+    for (int s = 1; s < splits; ++s) acc += p[(size_t)s * split_stride];
+    return acc;
+}
+
+template <typename T>
+__global__ void norm_add_kernel(float* __restrict__ resid, const void* __restrict__ y, const float* __restrict__ w,
+                                T* __restrict__ copy, int H, float eps, int splits, long long split_stride) {
+    extern __shared__ float srow[];  // H floats + 33 scratch
+    float* scratch = srow + H;
+    const size_t r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = load_sum<T>(y, r * H + i, splits, split_stride);
+        srow[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = resid[r * H + i] + srow[i] * rinv * w[i];
+        resid[r * H + i] = v;
+        if (copy) copy[r * H + i] = from_float<T>(v);
+    }
+}
+
+LLMK_EXPORT int llmk_norm_add(float* resid, const void* y, const float* w, void* copy, int n_rows, int H, float eps,
+                              int splits, long long split_stride, int dtype, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (H <= 0 || !y || !w || !resid) LLMK_FAIL("norm_add: bad arguments (H %d)", H);
+    const size_t smem = ((size_t)H + 33) * sizeof(float);
+    if (smem > 200 * 1024) LLMK_FAIL("norm_add: a row of %d values does not fit shared memory", H);
+    const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(norm_add_kernel<float>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (float*)copy, H, eps, splits, split_stride);
+    } else if (dtype == LLMK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(norm_add_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (bf16*)copy, H, eps, splits, split_stride);
+    } else
+        LLMK_FAIL("norm_add: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("norm_add", e);
+    return LLMK_OK;
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ out, const float* __restrict__ in, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_float<T>(in[i]);
+}
+
+LLMK_EXPORT int llmk_cast_rows(void* out, const float* in, long long n, int dtype, void* stream) {
+    if (n <= 0) return LLMK_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(cast_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, in, n);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(cast_rows_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, in, n);
+    else
+        LLMK_FAIL("cast_rows: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("cast_rows", e);
+    return LLMK_OK;
+}
+
+// mode 0: out[r, f] = relu(x[r, f])^2, x [n, F]
+// mode 1: x [n, 2F], gate in columns [0, F), up in [F, 2F):
+//         g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)
+enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1 };
+
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x, int n, int F, long long ld, int mode,
+                                float alpha, float limit, int splits, long long split_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)n * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const size_t r = (size_t)(i / F);
+        const int f = (int)(i % F);
+        float v;
+        if (mode == ACT_RELU2) {
+            const float a = fmaxf(load_sum<T>(x, r * ld + f, splits, split_stride), 0.f);
+            v = a * a;
+        } else {
+            const float g = fminf(load_sum<T>(x, r * ld + f, splits, split_stride), limit);
+            const float u = fminf(fmaxf(load_sum<T>(x, r * ld + F + f, splits, split_stride), -limit), limit);
+            v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+        }
+        out[i] = from_float<T>(v);
+    }
+}
+
+LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long ld, int mode, float alpha, float limit,
+                              int splits, long long split_stride, int dtype, void* stream) {
+    if (n <= 0 || F <= 0) return LLMK_OK;
+    if (mode != ACT_RELU2 && mode != ACT_CLAMPED_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
+    long long blocks = ((long long)n * F + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(act_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(act_rows_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride);
+    else
+        LLMK_FAIL("act_rows: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("act_rows", e);
+    return LLMK_OK;
+}
+
+// out[r, i] = o[r, i] * (w ? rsqrt(mean(o[r, :]^2) + eps) * w[i] : 1) * sigmoid(g[r, i]); o float32 [n, H], g of T with rows
+// `ldg` apart.
+template <typename T>
+__global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g,
+                                     const float* __restrict__ w, int H, long long ldg, float eps) {
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    float rinv = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = o[r * H + i];
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    }
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float gate = 1.0f / (1.0f + expf(-to_float(g[r * ldg + i])));
+        out[r * H + i] = from_float<T>(o[r * H + i] * rinv * (w ? w[i] : 1.f) * gate);
+    }
+}
+
+LLMK_EXPORT int llmk_gated_rmsnorm(void* out, const float* o, const void* g, const float* w, int n_rows, int H, long long ldg,
+                                   float eps, int dtype, void* stream) {
+    if (n_rows <= 0 || H <= 0) return LLMK_OK;
+    const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, true, (float*)out, o, (const float*)g, w, H, ldg, eps);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(gated_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, true, (bf16*)out, o, (const bf16*)g, w, H, ldg, eps);
+    else
+        LLMK_FAIL("gated_rmsnorm: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("gated_rmsnorm", e);
+    return LLMK_OK;
+}

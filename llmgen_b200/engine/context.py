@@ -171,6 +171,7 @@ class StepContext:
     extra: Dict[str, torch.Tensor] = field(default_factory=dict)
     fixed_shapes: bool = False   # True inside graph capture/replay: choose launch shapes from bounds
     max_seqs_bound: int = 0      # most sequences any step of this engine has
+    stream_copy_of: object = None   # the residual buffer whose rows the workspace's "stream_copy" holds in the storage dtype
 
     def array(self, name: str) -> torch.Tensor:
         return self.extra[name]

@@ -49,6 +49,10 @@ MODULES: Dict[str, List[str]] = {
     "attention_decode": [],
     "attention_tc": [],
     "sampling": [],
+    "rowwise": [],
+    "linear_attention": [],
+    "latent_attention": [],
+    "moe": [],
     "runtime": [],      # host code only: cache manager, scheduler, step arrays
 }
 

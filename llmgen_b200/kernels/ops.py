@@ -662,3 +662,207 @@ def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, see
         raise KernelError("sample: one 64-bit key per row is required")
     _check(lib, lib.llmk_sample(_ptr(out_ids), _ptr(logits), c_longlong(_row_stride(logits)), _ptr(temps),
                                 _ptr(seed), _ptr(row_keys), c_int(n), c_int(V), _ptr(scratch), c_int(rows), _stream()))
+
+
+# ---------------------------------------------------------------------- rows of post-norm layers
+ACTIVATIONS = {"relu2": 0, "clamped_glu": 1}
+
+
+def _delta_args(y, dtype: torch.dtype):
+    """(pointer source, splits, split stride) of a product's result: an array of `dtype`, or float32 slices."""
+    if isinstance(y, Partials):
+        return y.tensor, y.splits, y.split_stride
+    if y.dtype != dtype or not y.is_contiguous():
+        raise KernelError("a product's result must be contiguous and of the storage dtype (or float32 slices)")
+    return y, 0, 0
+
+
+def norm_add(resid: torch.Tensor, y, weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor], dtype: torch.dtype) -> None:
+    """resid (float32 [n, H]) += rmsnorm(y) * weight; `copy` (storage dtype [n, H], or None) receives the new rows.
+    `y` is an array of the storage dtype or a `Partials`."""
+    lib = build.load("rowwise")
+    n, H = resid.shape
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("norm_add: residual and gain must be float32")
+    src, splits, stride = _delta_args(y, dtype)
+    rows = y.rows if isinstance(y, Partials) else y.shape[0]
+    if rows != n or (copy is not None and (copy.dtype != dtype or tuple(copy.shape) != (n, H) or not copy.is_contiguous())):
+        raise KernelError("norm_add: shapes do not fit")
+    _check(lib, lib.llmk_norm_add(_ptr(resid), _ptr(src), _ptr(weight), _ptr(copy), c_int(n), c_int(H), c_float(eps),
+                                  c_int(splits), c_longlong(stride), c_int(dtype_code(dtype)), _stream()))
+
+
+def cast_rows(out: torch.Tensor, src: torch.Tensor) -> None:
+    """out (storage dtype, contiguous) = src (float32, contiguous), element by element."""
+    lib = build.load("rowwise")
+    if src.dtype != torch.float32 or not src.is_contiguous() or not out.is_contiguous() or out.numel() != src.numel():
+        raise KernelError("cast_rows: contiguous float32 in, as many values out")
+    _check(lib, lib.llmk_cast_rows(_ptr(out), _ptr(src), c_longlong(src.numel()), c_int(dtype_code(out.dtype)), _stream()))
+
+
+def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: float = 0.0) -> None:
+    """out[n, F] = relu(x)^2 ("relu2", x [n, F]) or the clamped gated unit of x [n, 2F] ("clamped_glu": gate in
+    the first F columns, up in the last): g' = min(g, limit), u' = clamp(u, -limit, limit),
+    out = g' sigmoid(alpha g') (u' + 1).  `x` is an array or a `Partials`."""
+    lib = build.load("rowwise")
+    try:
+        mode = ACTIVATIONS[activation]
+    except KeyError:
+        raise KernelError(f"unknown activation {activation!r} (known: {', '.join(ACTIVATIONS)})") from None
+    n, F = out.shape
+    if isinstance(x, Partials):
+        src, splits, stride, ld = x.tensor, x.splits, x.split_stride, x.cols
+    else:
+        src, splits, stride, ld = x, 0, 0, _row_stride(x)
+        if x.dtype != out.dtype:
+            raise KernelError("act_rows: input and output share the storage dtype")
+    _check(lib, lib.llmk_act_rows(_ptr(out), _ptr(src), c_int(n), c_int(F), c_longlong(ld), c_int(mode), c_float(alpha), c_float(limit),
+                                  c_int(splits), c_longlong(stride), c_int(dtype_code(out.dtype)), _stream()))
+
+
+def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> None:
+    """out[n, H] (storage dtype) = rmsnorm(o) * weight * sigmoid(gate); o float32 [n, H] contiguous, gate of the storage
+    dtype with any row stride.  Without `weight`: o * sigmoid(gate)."""
+    lib = build.load("rowwise")
+    n, H = out.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or gate.dtype != out.dtype:
+        raise KernelError("gated_rmsnorm: o must be contiguous float32 and the gate of the storage dtype")
+    _check(lib, lib.llmk_gated_rmsnorm(_ptr(out), _ptr(o), _ptr(gate), _ptr(weight), c_int(n), c_int(H), c_longlong(_row_stride(gate)),
+                                       c_float(eps), c_int(dtype_code(out.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------------ linear attention
+def linear_attention(out: torch.Tensor, packed: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor,
+                     decay: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, heads: int, dim: int,
+                     vdim: int, silu: bool = True) -> None:
+    """The decayed outer-product recurrence over each sequence's new tokens (csrc/linear_attention.cu).  `packed`
+    [tokens, >= ...] holds q, k (heads x dim) and v (heads x vdim) at the column offsets given; `state` float32
+    [slots, heads, dim, vdim] is read and written at each sequence's slot; out float32 [tokens, heads * vdim]."""
+    lib = build.load("linear_attention")
+    if out.dtype != torch.float32 or state.dtype != torch.float32 or decay.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("linear_attention: out, state and decay are float32")
+    if tuple(state.shape[1:]) != (heads, dim, vdim) or not state.is_contiguous():
+        raise KernelError(f"linear_attention: state must be [slots, {heads}, {dim}, {vdim}], got {list(state.shape)}")
+    es = packed.element_size()
+    base = packed.data_ptr()
+    _check(lib, lib.llmk_linear_attention(_ptr(out), c_void_p(base + q_off * es), c_void_p(base + k_off * es), c_void_p(base + v_off * es),
+                                          c_longlong(_row_stride(packed)), _ptr(state), _ptr(decay), _ptr(cu_q), _ptr(state_slots),
+                                          c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_int(1 if silu else 0),
+                                          c_int(dtype_code(packed.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------------ latent attention
+def latent_prep(packed: torch.Tensor, dq_off: int, dkv_off: int, q_rank: int, rank: int, rot: int, q_gain: Optional[torch.Tensor],
+                kv_gain: torch.Tensor, eps: float, cq_out: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                positions: torch.Tensor, slots: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                pairing: str) -> None:
+    """Per token of `packed` [n, ...]: cq_out[n, q_rank] = rmsnorm(packed[:, dq_off:+q_rank]) * q_gain, and the cached
+    vector [rmsnorm(c) * kv_gain | rotate(kr)] written at `slots` (csrc/latent_attention.cu)."""
+    lib = build.load("latent_attention")
+    n = packed.shape[0]
+    _check(lib, lib.llmk_latent_prep(_ptr(packed), c_longlong(_row_stride(packed)), c_int(dq_off), c_int(dkv_off), c_int(q_rank),
+                                     c_int(rank), c_int(rot), _ptr(q_gain), _ptr(kv_gain), c_float(eps), _ptr(cq_out), _ptr(cache),
+                                     _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), c_int(pairing_code(pairing)), c_int(n),
+                                     c_int(dtype_code(packed.dtype)), _stream()))
+
+
+def latent_absorb(qa: torch.Tensor, q: torch.Tensor, wuk: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                  sin: Optional[torch.Tensor], heads: int, dim: int, rot: int, rank: int, pairing: str) -> None:
+    """qa float32 [n, heads, rank + rot] = [Wuk_h^T q_unrotated | rotate(q_rotated)] of q [n, heads * (dim + rot)]."""
+    lib = build.load("latent_attention")
+    n = q.shape[0]
+    if qa.dtype != torch.float32 or not qa.is_contiguous() or qa.numel() != n * heads * (rank + rot) or wuk.dtype != q.dtype:
+        raise KernelError("latent_absorb: shapes or dtypes do not fit")
+    _check(lib, lib.llmk_latent_absorb(_ptr(qa), _ptr(q), c_longlong(_row_stride(q)), _ptr(wuk), _ptr(positions), _ptr(cos), _ptr(sin),
+                                       c_int(n), c_int(heads), c_int(dim), c_int(rot), c_int(rank), c_int(pairing_code(pairing)),
+                                       c_int(dtype_code(q.dtype)), _stream()))
+
+
+def latent_attention_tile_queries(heads: int) -> int:
+    return int(build.load("latent_attention").llmk_latent_attention_tile_queries(c_int(heads)))
+
+
+def latent_attention_scratch_floats(n_tokens: int, heads: int, rank: int, parts: int) -> int:
+    return 0 if parts <= 1 else n_tokens * heads * parts * (rank + 2)
+
+
+def latent_attention(out: torch.Tensor, qa: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, max_blocks: int,
+                     ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tokens: int,
+                     heads: int, rank: int, rot: int, page_size: int, scale: float, parts: int = 1,
+                     scratch: Optional[torch.Tensor] = None) -> None:
+    """out float32 [n, heads, rank] = causal softmax attention of qa over the cached vectors (one shared kv head whose
+    values are the first `rank` entries of the cached vector)."""
+    lib = build.load("latent_attention")
+    if out.dtype != torch.float32 or qa.dtype != torch.float32:
+        raise KernelError("latent_attention: queries and outputs are float32")
+    if parts > 1 and (scratch is None or scratch.numel() < latent_attention_scratch_floats(n_tokens, heads, rank, parts)):
+        raise KernelError("latent_attention: scratch too small")
+    _check(lib, lib.llmk_latent_attention(_ptr(out), _ptr(qa), _ptr(cache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len),
+                                          _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(tile_seq.numel()), c_int(n_tokens),
+                                          c_int(heads), c_int(rank), c_int(rot), c_int(page_size), c_float(scale), c_int(parts),
+                                          _ptr(scratch), c_int(dtype_code(cache.dtype)), _stream()),
+           2 if parts > 1 else 1)
+
+
+def latent_expand(out: torch.Tensor, oa: torch.Tensor, wuv: torch.Tensor, gate: Optional[torch.Tensor], heads: int, rank: int,
+                  vdim: int) -> None:
+    """out[n, heads * vdim] (storage dtype) = (Wuv_h oa[n, h]) * sigmoid(gate)."""
+    lib = build.load("latent_attention")
+    n = out.shape[0]
+    if oa.dtype != torch.float32 or wuv.dtype != out.dtype or (gate is not None and gate.dtype != out.dtype):
+        raise KernelError("latent_expand: dtypes do not fit")
+    _check(lib, lib.llmk_latent_expand(_ptr(out), _ptr(oa), _ptr(wuv), _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0),
+                                       c_int(n), c_int(heads), c_int(rank), c_int(vdim), c_int(dtype_code(out.dtype)), _stream()))
+
+
+# -------------------------------------------------------------------------- routed feed-forward
+ROUTER_SCORINGS = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_max_tiles(n_slots: int, experts: int) -> int:
+    return int(build.load("moe").llmk_moe_max_tiles(c_int(n_slots), c_int(experts)))
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, slot_expert: torch.Tensor, slot_weight: torch.Tensor, top: int,
+              scoring: str = "sigmoid", renormalize: bool = False) -> None:
+    """Per row of h [n, K]: scores of router (float32 [E, K]) h, the `top` largest choose; slot n * top + c receives
+    (expert, score)."""
+    lib = build.load("moe")
+    n, K = h.shape
+    E = router.shape[0]
+    if router.dtype != torch.float32 or slot_expert.dtype != torch.int32 or slot_weight.dtype != torch.float32:
+        raise KernelError("moe_route: router and weights float32, experts int32")
+    _check(lib, lib.llmk_moe_route(_ptr(h), c_longlong(_row_stride(h)), _ptr(router), _ptr(slot_expert), _ptr(slot_weight), c_int(n),
+                                   c_int(K), c_int(E), c_int(top), c_int(ROUTER_SCORINGS[scoring]), c_int(1 if renormalize else 0),
+                                   c_int(dtype_code(h.dtype)), _stream()))
+
+
+def moe_plan(slot_expert: torch.Tensor, n_slots: int, experts: int, order: torch.Tensor, pos_of_slot: torch.Tensor,
+             tile_expert: torch.Tensor, tile_start: torch.Tensor, tile_rows: torch.Tensor) -> None:
+    lib = build.load("moe")
+    _check(lib, lib.llmk_moe_plan(_ptr(slot_expert), c_int(n_slots), c_int(experts), _ptr(order), _ptr(pos_of_slot), _ptr(tile_expert),
+                                  _ptr(tile_start), _ptr(tile_rows), _stream()))
+
+
+def moe_experts(out: torch.Tensor, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], order: torch.Tensor,
+                slot_weight: torch.Tensor, tile_expert: torch.Tensor, tile_start: torch.Tensor, tile_rows: torch.Tensor,
+                n_slots: int, top: int, first: bool, weight_on_input: bool, alpha: float = 1.0, limit: float = 0.0) -> None:
+    """first: out float32 [slots, ff] = gated activation of the rows' products with w0 = gate, w1 = up [E, ff, K];
+    else out float32 [slots, K] = rows of x (float32 [slots, ff]) times w0 = down [E, K, ff]."""
+    lib = build.load("moe")
+    E, N, K = w0.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.shape[1] != N:
+        raise KernelError("moe_experts: out is contiguous float32 [slots, columns]")
+    _check(lib, lib.llmk_moe_experts(_ptr(out), _ptr(x), c_longlong(_row_stride(x)), _ptr(w0), _ptr(w1), _ptr(order), _ptr(slot_weight),
+                                     _ptr(tile_expert), _ptr(tile_start), _ptr(tile_rows), c_int(n_slots), c_int(E), c_int(top),
+                                     c_int(K), c_int(N), c_int(1 if first else 0), c_int(1 if weight_on_input else 0), c_float(alpha),
+                                     c_float(limit), c_int(dtype_code(w0.dtype)), _stream()))
+
+
+def moe_combine(out: torch.Tensor, rows: torch.Tensor, pos_of_slot: torch.Tensor, shared_out: Optional[torch.Tensor], top: int) -> None:
+    """out float32 [n, H] = shared_out (storage dtype, or None) + the token's `top` rows of `rows` (float32 [slots, H])."""
+    lib = build.load("moe")
+    n, H = out.shape
+    dt = shared_out.dtype if shared_out is not None else torch.float32
+    _check(lib, lib.llmk_moe_combine(_ptr(out), _ptr(rows), _ptr(pos_of_slot), _ptr(shared_out), c_int(n), c_int(top), c_int(H),
+                                     c_int(dtype_code(dt)), _stream()))

@@ -11,6 +11,34 @@ from .registry import build_position, norm_class, register_mixer
 from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
 
 
+def add_query_tiles(builder, bq: int, window: int = 0, heaviest_first: bool = False) -> str:
+    """Adds to a step's arrays the (sequence, first query) of every tile of `bq` queries, under the name it returns
+    (with `_seq` and `_q0` appended); mixers that cut their queries the same way share one pair of arrays.
+    `heaviest_first`: in the order of the keys a tile has to read, most first; the blocks of a launch start in the
+    order of the list, and a prompt's last tiles read the whole prompt while its first read one tile of keys."""
+    name = f"attention_tiles_bq{bq}"
+    if builder.has(name + "_seq"):
+        return name
+    tiles = []
+    bound = getattr(builder, "token_bound", 0)
+    for s, n in enumerate(builder.q_lens):
+        if bound and n == 0:
+            continue
+        for start in range(0, max(n, 1), bq):
+            keys = builder.starts[s] + min(start + bq, max(n, 1))
+            tiles.append((min(keys, window + bq) if window else keys, s, start))
+    if heaviest_first:
+        tiles.sort(key=lambda t: -t[0])
+    if bound:
+        # a list of fixed length for the step's shape: no more tiles than this exist for `bound` tokens in
+        # `n_seqs` sequences; the rest is padding (sequence -1), which the kernels skip
+        most = bound // bq + builder.n_seqs
+        tiles += [(0, -1, 0)] * (most - len(tiles))
+    builder.add(name + "_seq", [t[1] for t in tiles])
+    builder.add(name + "_q0", [t[2] for t in tiles])
+    return name
+
+
 class GQAAttention(Mixer):
     """q, k, v projections (packed into one [(nq + 2 nkv) hd, H] matrix at load) -> per-head
     RMSNorm of q and k, rotary encoding, cache write (one kernel) -> attention over the block
@@ -89,29 +117,7 @@ class GQAAttention(Mixer):
         return self.position.max_positions if self.position is not None else None
 
     def _tiles(self, builder, bq: int, heaviest_first: bool = False) -> None:
-        """(sequence, first query) of every tile of `bq` queries.  `heaviest_first`: in the order of
-        the keys a tile has to read, most first; the blocks of a launch start in the order of the
-        list, and a prompt's last tiles read the whole prompt while its first read one tile of keys."""
-        name = f"attention_tiles_bq{bq}"
-        if builder.has(name + "_seq"):
-            return
-        tiles = []
-        bound = getattr(builder, "token_bound", 0)
-        for s, n in enumerate(builder.q_lens):
-            if bound and n == 0:
-                continue
-            for start in range(0, max(n, 1), bq):
-                keys = builder.starts[s] + min(start + bq, max(n, 1))
-                tiles.append((min(keys, self.window + bq) if self.window else keys, s, start))
-        if heaviest_first:
-            tiles.sort(key=lambda t: -t[0])
-        if bound:
-            # a list of fixed length for the step's shape: no more tiles than this exist for `bound` tokens in
-            # `n_seqs` sequences; the rest is padding (sequence -1), which the kernels skip
-            most = bound // bq + builder.n_seqs
-            tiles += [(0, -1, 0)] * (most - len(tiles))
-        builder.add(name + "_seq", [t[1] for t in tiles])
-        builder.add(name + "_q0", [t[2] for t in tiles])
+        add_query_tiles(builder, bq, self.window, heaviest_first)
 
     def tc_tile_queries(self, page_size: int) -> int:
         if self.dtype != torch.bfloat16:

@@ -70,9 +70,12 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     v_head_dim: int = 0      # width of a value where it differs from a key's (0: the same)
+    values: bool = True      # False: one array per token only (a mixer that reads keys and values out of one entry)
 
     @property
     def value_dim(self) -> int:
+        if not self.values:
+            return 0
         return self.v_head_dim or self.head_dim
 
 

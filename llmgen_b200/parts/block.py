@@ -6,7 +6,8 @@ import torch
 from .base import LayerCache, Part
 from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward_class, mixer_class, norm_class,
                        register_block)
-from .spec import PreNormBlockSpec
+from ..kernels import ops
+from .spec import PostNormBlockSpec, PreNormBlockSpec
 
 
 class PreNormBlock(Part):
@@ -56,4 +57,71 @@ class PreNormBlock(Part):
         return self.ffn.forward(ctx, x)
 
 
+class PostNormBlock(Part):
+    """x1 = x + norm(mixer(x)); x2 = x1 + norm(ffn(x1)): the norm sits on each sublayer's output, and the sublayers read the
+    residual stream itself.
+
+    The residual stream is the same float32 buffer as in every other block.  `norm_add` normalises a sublayer's output
+    (an array or the float32 slices of a product cut along K), adds it to the residual and, in bfloat16, leaves a copy of
+    the new residual rows in the storage dtype for the products of the sublayer that follows (the next block's mixer
+    included: the copy is kept in a workspace buffer that blocks of this kind share).  The block finishes both sums
+    itself and hands on nothing to add.  A block without a feed-forward stops after the first sum."""
+
+    @staticmethod
+    def weight_decls(spec: PostNormBlockSpec):
+        decls = norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm) + mixer_class(spec.mixer).weight_decls(spec.mixer)
+        if spec.ffn is not None:
+            decls += norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm) + feed_forward_class(spec.ffn).weight_decls(spec.ffn)
+        return decls
+
+    @staticmethod
+    def kernel_modules(spec: PostNormBlockSpec):
+        mods = ("rowwise",) + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer))
+        if spec.ffn is not None:
+            mods += tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn))
+        return mods
+
+    def __init__(self, spec: PostNormBlockSpec, weights, dtype, device):
+        for norm in (spec.mixer_norm, spec.ffn_norm if spec.ffn is not None else None):
+            if norm is not None and (norm.kind != "rmsnorm" or norm.weight_offset != 0.0):
+                raise ValueError("post-norm block: the norms on the sublayers' outputs are plain RMSNorms")
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = build_norm(spec.mixer_norm, weights, dtype, device)
+        self.mixer = build_mixer(spec.mixer, weights, dtype, device)
+        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device) if spec.ffn is not None else None
+        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device) if spec.ffn is not None else None
+
+    def workspace_bytes(self, tokens: int) -> int:
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        own = tokens * self.spec.mixer_norm.dim * elem
+        parts = [getattr(p, "workspace_bytes", None) for p in (self.mixer, self.ffn) if p is not None]
+        return own + max([f(tokens) for f in parts if f is not None] or [0])
+
+    def _stream_copy(self, ctx, resid):
+        """The residual rows as the products read them: the float32 buffer itself, or its copy in bfloat16."""
+        if self.dtype == torch.float32:
+            return resid, None
+        T, H = resid.shape
+        return None, ctx.workspace.buffer("stream_copy", T, H, self.dtype)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
+        x, copy = self._stream_copy(ctx, resid)
+        if delta is not None or getattr(ctx, "stream_copy_of", None) is not resid:
+            # the block before was of another kind (or this is the first one): finish its sum, make the copy
+            if delta is not None:
+                resid.add_(delta.sum() if isinstance(delta, ops.Partials) else delta.float())
+            if copy is not None:
+                ops.cast_rows(copy, resid)
+            ctx.stream_copy_of = resid
+        x = resid if copy is None else copy
+        mixed = self.mixer.forward(ctx, x, cache)
+        ops.norm_add(resid, mixed, self.mixer_norm.weight, self.mixer_norm.eps, copy, self.dtype)
+        if self.ffn is not None:
+            out = self.ffn.forward(ctx, x)
+            ops.norm_add(resid, out, self.ffn_norm.weight, self.ffn_norm.eps, copy, self.dtype)
+        return None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("postnorm", PostNormBlock)

@@ -129,4 +129,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from . import attention, block, mlp, norm, rope  # noqa: F401
+        from . import attention, block, latent_attention, linear_attention, mlp, moe, norm, rope  # noqa: F401

@@ -53,8 +53,8 @@ class RMSNormSpec:
 class RopeSpec:
     """Rotary position encoding over the first `rotary_dim` values of a head, angle =
     pos / theta^(2i/rotary_dim).  `pairing` says which two values are turned together: "half" is the
-    half-split (NEOX) pairing (i, i + rotary_dim/2) of the reference; the attention kernels are told
-    the pairing and refuse one they do not implement.
+    half-split (NEOX) pairing (i, i + rotary_dim/2) of the reference, "interleaved" the pairing (2i, 2i + 1); a mixer's
+    kernels are told the pairing and refuse one they do not implement.
 
     Reference: src/module/rope.zig:60-107, src/backend/cpu/rope.zig:13-75.
     """
@@ -93,7 +93,101 @@ class AttentionSpec:
     kind: str = "attention"
 
 
+@dataclass(frozen=True)
+class LinearAttentionSpec:
+    """Linear attention with a decay per head and a state carried from token to token.
+
+    q = act(x Wq^T), k = act(x Wk^T) [heads, key_dim], v = act(x Wv^T) [heads, value_dim]; per head
+    S_t = decay_h S_(t-1) + k_t (x) v_t (float32, zero when the request starts), o_t = S_t^T q_t, no other scale.
+    The heads side by side pass an RMSNorm (`out_norm`, optional), are multiplied by sigmoid(x Wg^T) (`gate_proj`,
+    optional) and projected by Wo.  The state [heads, key_dim, value_dim] lives in the cache manager's state slots.
+    """
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]             # one factor per head
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    o_proj: str
+    gate_proj: Optional[str] = None
+    out_norm: Optional[RMSNormSpec] = None
+    activation: str = "silu"             # on q, k and v: "silu" or "none"
+    kind: str = "linear_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are expanded from a cached latent vector per token.
+
+    Queries through a latent of their own: cq = norm(x Wdq^T), q = cq Wuq^T, per head [nope_dim | rope_dim].
+    x Wdkv^T has kv_rank + rope_dim values: the first kv_rank, normed, are the latent c; the last rope_dim are one
+    rotated key part shared by all heads.  Head h: key [Wuk_h c | rotated part], value Wuv_h c (value_dim);
+    score = (q . key) * scale.  The heads side by side are multiplied by sigmoid(x Wg^T) (`gate_proj`, optional) and
+    projected by Wo.  Only [c | rotated part] is cached (one shared entry of kv_rank + rope_dim values per token).
+    """
+    hidden_size: int
+    num_heads: int
+    nope_dim: int
+    rope_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    dq_proj: str
+    uq_proj: str
+    dkv_proj: str
+    uk_proj: str
+    uv_proj: str
+    o_proj: str
+    q_norm: RMSNormSpec
+    kv_norm: RMSNormSpec
+    position: Optional[RopeSpec] = None
+    gate_proj: Optional[str] = None
+    kind: str = "latent_attention"
+
+
 # ---------------------------------------------------------------------- feed-forwards
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """Feed-forward without a gate: down( act(x Wup^T) ), act = relu(.)^2 ("relu2")."""
+    hidden_size: int
+    intermediate_size: int
+    up_proj: str
+    down_proj: str
+    activation: str = "relu2"
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
+class ClampedExpertSpec:
+    """One small gated feed-forward with clamped branches: g = min(x Wgate^T, limit), u = clamp(x Wup^T, -limit, limit),
+    y = g sigmoid(alpha g) (u + 1), output y Wdown^T; no biases."""
+    intermediate_size: int
+    limit: float
+    gate_proj: str
+    up_proj: str
+    down_proj: str
+    alpha: float = 1.702
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """Mixture of experts: router scores s = sigmoid(x Wr^T) (or softmax) in float32, the `top_k` largest choose
+    experts, their scores are the weights (renormalised over the chosen ones if `renormalize`).  The weight multiplies
+    the expert's input (`weight_on_input`) or its output.  An optional shared expert runs for every token and is added."""
+    hidden_size: int
+    router: str
+    experts: Tuple[ClampedExpertSpec, ...]
+    top_k: int
+    shared: Optional[ClampedExpertSpec] = None
+    scoring: str = "sigmoid"
+    renormalize: bool = False
+    weight_on_input: bool = True
+    kind: str = "routed_mlp"
+
+
 @dataclass(frozen=True)
 class GatedMLPSpec:
     """Dense gated feed-forward: down( act(x Wg^T) * (x Wu^T) ).
@@ -122,6 +216,17 @@ class PreNormBlockSpec:
     ffn_norm: object
     ffn: object
     kind: str = "prenorm"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """x1 = x + norm(mixer(x)); x2 = x1 + norm(ffn(x1)): the norms sit on the sublayers' outputs and the sublayers
+    read the residual stream itself.  `ffn` (and `ffn_norm`) may be None: a layer without a feed-forward."""
+    mixer_norm: object
+    mixer: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    kind: str = "postnorm"
 
 
 @dataclass(frozen=True)
