@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
                     [--shape 0.6b|8b|32b --layers L]      (other layer sizes, beside the default run)
     python bench.py --kernels [--kernels-out FILE.md]     (kernel by kernel beside the reference's own kernels)
+    python bench.py --designs [--designs-out FILE.md]     (Derupel beside Qwen3 at equal layer sizes)
 
 Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
 prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
@@ -211,6 +212,11 @@ def main():
     ap.add_argument("--kernels", action="store_true",
                     help="time this engine's kernels beside the reference's (baseline/_ref, built by baseline/build_reference_kernels.py)")
     ap.add_argument("--kernels-out", default="", help="with --kernels: also write the table as markdown to this file")
+    ap.add_argument("--designs", action="store_true",
+                    help="Derupel beside Qwen3 at equal layer sizes: prefill and decode throughput and every kernel's share of the "
+                         "measured peaks (baseline/design_compare.py); prints one JSON line of its own")
+    ap.add_argument("--designs-size", default="", help="with --designs: only these sizes (comma-separated; default all)")
+    ap.add_argument("--designs-out", default="", help="with --designs: also write the tables as markdown to this file")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -221,6 +227,19 @@ def main():
         return 0
     if args.kernels:
         return kernels_table(args)
+    if args.designs:
+        from baseline import design_compare
+        from llmgen_b200.engine.api import require_cuda
+        require_cuda()
+        sampler = ClockSampler()
+        sampler.start()
+        result = design_compare.run(args, ROOT, sampler)
+        if args.designs_out:
+            os.makedirs(os.path.dirname(os.path.abspath(args.designs_out)), exist_ok=True)
+            with open(args.designs_out, "w") as f:
+                f.write(design_compare.as_markdown(result) + "\n")
+        print(json.dumps(result))
+        return 0
     if args.rates:
         from baseline import device_rates
         sys.stdout.write(device_rates.run())

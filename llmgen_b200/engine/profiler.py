@@ -301,8 +301,58 @@ def _cost_all_operands(a, info: PassInfo) -> Tuple[int, int]:
     return flops, sum(_nbytes(v) for k, v in a.items() if k != "scratch")
 
 
+def _cost_linear_attention(a, info: PassInfo) -> Tuple[int, int]:
+    heads, dim, vdim = int(a["heads"]), int(a["dim"]), int(a["vdim"])
+    tokens, seqs = sum(info.q_lens), len(info.q_lens)
+    chunk = 32                                             # scores inside a chunk, the state's share, the state's update
+    flops = tokens * heads * (4 * dim * vdim + min(chunk, max(info.q_lens or (1,))) * (dim + vdim))
+    elem = a["packed"].element_size()
+    bytes_ = tokens * heads * ((2 * dim + vdim) * elem + vdim * 4) + 2 * seqs * heads * dim * vdim * 4
+    return flops, bytes_
+
+
+def _cost_latent_attention(a, info: PassInfo) -> Tuple[int, int]:
+    heads, rank, rot = int(a["heads"]), int(a["rank"]), int(a["rot"])
+    tokens = sum(info.q_lens)
+    flops = 2 * heads * (2 * rank + rot) * info.visible_keys(0)
+    bytes_ = (rank + rot) * a["cache"].element_size() * info.keys_read(0) + tokens * heads * (2 * rank + rot) * 4
+    return flops, bytes_
+
+
+def _cost_latent_absorb(a, info: PassInfo) -> Tuple[int, int]:
+    n = int(a["q"].shape[0])
+    return 2 * n * int(a["heads"]) * int(a["dim"]) * int(a["rank"]), _nbytes(a["q"]) + _nbytes(a["qa"]) + _nbytes(a["wuk"])
+
+
+def _cost_latent_expand(a, info: PassInfo) -> Tuple[int, int]:
+    n = int(a["out"].shape[0])
+    return 2 * n * int(a["heads"]) * int(a["rank"]) * int(a["vdim"]), 2 * _nbytes(a["out"]) + _nbytes(a["oa"]) + _nbytes(a["wuv"])
+
+
+def _cost_latent_prep(a, info: PassInfo) -> Tuple[int, int]:
+    n, elem = int(a["packed"].shape[0]), a["packed"].element_size()
+    values = int(a["q_rank"]) + int(a["rank"]) + int(a["rot"])
+    return 6 * n * values, 2 * n * values * elem
+
+
+def _cost_moe_route(a, info: PassInfo) -> Tuple[int, int]:
+    n, K = a["h"].shape
+    return 2 * int(n) * int(K) * int(a["router"].shape[0]), _nbytes(a["h"]) + _nbytes(a["router"])
+
+
+def _cost_moe_experts(a, info: PassInfo) -> Tuple[int, int]:
+    E, N, K = (int(v) for v in a["w0"].shape)
+    slots, both = int(a["n_slots"]), 2 if a["first"] else 1
+    touched = min(E, slots)                                # every expert's matrices are read at most once per tile
+    return 2 * slots * N * K * both, touched * N * K * both * a["w0"].element_size() + slots * (N + K) * 4
+
+
 # kernel bindings of `ops` that launch work, and how each one's FLOPs and bytes are counted
 OP_COSTS: Dict[str, Callable] = {
+    "norm_add": _cost_all_operands, "cast_rows": _cost_all_operands, "act_rows": _cost_all_operands,
+    "gated_rmsnorm": _cost_all_operands, "linear_attention": _cost_linear_attention, "latent_prep": _cost_latent_prep,
+    "latent_absorb": _cost_latent_absorb, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
+    "moe_route": _cost_moe_route, "moe_experts": _cost_moe_experts, "moe_combine": _cost_all_operands,
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,
     "attn_prep": _cost_attn_prep, "gemm_simt": _cost_product, "gemv_bf16": _cost_product, "gemm_tc": _cost_product,
     "gemm_skinny": _cost_product, "gemm_rows8": _cost_product, "gemm_rows8_gated": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,

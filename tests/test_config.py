@@ -85,7 +85,7 @@ def test_unknown_architecture():
     d = dict(TINY_A, architectures=["NoSuchModel"])
     with pytest.raises(ConfigError, match="unknown architecture.*Qwen3ForCausalLM"):
         config_from_dict(d)
-    with pytest.raises(ConfigError, match="neither"):
+    with pytest.raises(ConfigError, match="names the model"):
         config_from_dict({"hidden_size": 4})
 
 
