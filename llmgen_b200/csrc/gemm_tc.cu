@@ -82,7 +82,8 @@ template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int store_by_tma, int splits,
-               TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag) {
+               TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag,
+               const int* __restrict__ tile_group) {
     static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
     using L = Smem<BN, STAGES, MB, PAIR, KS>;
     constexpr int ROWS = (PAIR ? 2 : MB) * BM;                     // rows of a tile
@@ -153,7 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // wait for the kernel that makes A, and arrive while that kernel ends.
             uint32_t w_ahead = 0;
             if constexpr (!PAIR) {
-                if (unit < total_items) {
+                if (unit < total_items && !tile_group) {      // (which rows of W a grouped tile reads is known only after the wait)
                     const int tile = unit % total_tiles, kb0 = (unit / total_tiles) * kb_per_split;
                     const int sts = (min(num_kb, kb0 + kb_per_split) - kb0 + KS - 1) / KS;     // stages of the first item
                     w_ahead = (uint32_t)(sts < STAGES ? sts : STAGES);
@@ -174,7 +175,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int item = unit; item < total_items && ok; item += units) {
                 const int tile = item % total_tiles, split = item / total_tiles;
                 const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM;
-                const int n0 = (tile / m_tiles) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
+                int n0 = (tile / m_tiles) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
+                if (tile_group) {
+                    // grouped: the 128 rows of this tile belong to one group, whose matrix is rows [g N, (g + 1) N) of W
+                    const int g = tile_group[tile % m_tiles];
+                    if (g < 0) continue;                       // a tile of padding: nobody computes, nobody stores it
+                    n0 += g * N;
+                }
                 const int kb_end = min(num_kb, (split + 1) * kb_per_split);
                 for (int kb = split * kb_per_split; kb < kb_end; kb += KS, ++it) {
                     const int s = it % STAGES;
@@ -226,7 +233,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
+            if (tile_group) pdl_wait();         // the list of groups comes from a kernel before this one
             for (int item = unit; item < total_items && ok; item += units, ++tile_iter) {
+                if (tile_group && tile_group[(item % total_tiles) % m_tiles] < 0) {
+                    --tile_iter;                // a tile of padding takes no turn with the accumulators
+                    continue;
+                }
                 const int split = item / total_tiles;
                 const int kb_begin = split * kb_per_split, kb_end = min(num_kb, (split + 1) * kb_per_split);
                 const int buf = tile_iter % ACC_SETS;
@@ -278,8 +290,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int tile_iter = 0;
         uint32_t box_iter = 0;          // boxes this warp has handed to TMA
+        if (tile_group) pdl_wait();
         for (int item = unit; item < total_items && ok; item += units, ++tile_iter) {
             const int tile = item % total_tiles, split = item / total_tiles;
+            if (tile_group && tile_group[tile % m_tiles] < 0) {
+                --tile_iter;
+                continue;
+            }
             const int buf = tile_iter % ACC_SETS;
             const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM, n0 = (tile / m_tiles) * BN;
             ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&acc_full[buf]), (tile_iter / ACC_SETS) & 1, abort_flag));
@@ -522,7 +539,7 @@ bool get_slice_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t c
 
 template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false, int KS = 1>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
-           int* error_flag, int pdl, cudaStream_t s, int splits = 1) {
+           int* error_flag, int pdl, cudaStream_t s, int splits = 1, const int* tile_group = nullptr) {
     using L = Smem<BN, STAGES, MB, PAIR, KS>;
     auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB, PAIR, KS>;
     static bool configured = false;   // per instantiation
@@ -548,12 +565,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
         const int pairs = tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch_clusters(kernel, dim3(2 * pairs), dim3(THREADS), L::TOTAL, s, pdl != 0,
                                                              dim3(2, 1, 1), ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K,
-                                                             ldc, error_flag));
+                                                             ldc, error_flag, tile_group));
     } else {
         const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM) * splits;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
                                                     pdl != 0, ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K, ldc,
-                                                    error_flag));
+                                                    error_flag, tile_group));
     }
     return LLMK_OK;
 }
@@ -650,6 +667,36 @@ LLMK_EXPORT int llmk_gemm_tc_sliced(float* C, const void* A, const void* W, int 
     if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, 128))
         LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
     return launch<float, 128, STAGES_128, false, 1, false, KS_128>(ma, mw, C, M, N, K, ldc, error_flag, pdl, (cudaStream_t)stream, splits);
+}
+
+// Grouped product: the rows of A come in tiles of 128 that belong to one group each (`tile_group[i]` for rows
+// [128 i, 128 i + 128); -1: a tile of padding, skipped), W stacks the groups' matrices ([groups * N, K]) and
+// C[m, :] = A[m, :] * W[group of m's tile]^T.  The list of groups lives on the device, so the launch has the same
+// shape whatever the groups' sizes are (a mixture of experts whose rows were sorted by expert on the device).
+LLMK_EXPORT int llmk_gemm_tc_grouped(void* C, const void* A, const void* W, int M, int N, int K, long long lda, long long ldw,
+                                     long long ldc, int groups, const int* tile_group, int out_dtype, int* error_flag, int pdl,
+                                     void* stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return LLMK_OK;
+    if (!llmk_gemm_tc_usable(A, W, M, N, K, lda, ldw))
+        LLMK_FAIL("gemm_tc_grouped: operands not usable (K=%d lda=%lld ldw=%lld must be multiples of 8, bases 16-byte aligned)", K, lda, ldw);
+    if (M % BM != 0 || !tile_group) LLMK_FAIL("gemm_tc_grouped: %d rows are not whole tiles of %d with a group each", M, BM);
+    if (ldc < N) LLMK_FAIL("gemm_tc_grouped: ldc=%lld too small", ldc);
+    const int bn = N >= 256 ? 256 : N > 64 ? 128 : 64;
+    CUtensorMap ma, mw;
+    if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, (uint64_t)groups * N, K, ldw, bn))
+        LLMK_FAIL("gemm_tc_grouped: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d groups=%d)", M, N, K, groups);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == LLMK_BF16) {
+        if (bn == 256) return launch<bf16, 256, 4, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+        if (bn == 128) return launch<bf16, 128, STAGES_128, false, 1, false, KS_128>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+        return launch<bf16, 64, STAGES_64, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+    }
+    if (out_dtype == LLMK_F32) {
+        if (bn == 256) return launch<float, 256, 4, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+        if (bn == 128) return launch<float, 128, STAGES_128, false, 1, false, KS_128>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+        return launch<float, 64, STAGES_64, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s, 1, tile_group);
+    }
+    LLMK_FAIL("gemm_tc_grouped: unknown output dtype %d", out_dtype);
 }
 
 LLMK_EXPORT void llmk_gemm_tc_set_pair_mode(int mode) { g_pair_mode = mode; }

@@ -6,7 +6,11 @@
 //   moe_plan      one block: slots grouped by expert, cut into tiles of TT rows of one expert each; the list of tiles
 //                 has a fixed length (slots / TT + experts), padded with expert -1
 //   moe_experts   grid (tiles, column blocks): first product of a tile's rows with its expert's matrices and the
-//                 gated activation, or the second product (down); float32 sums on the CUDA cores
+//                 gated activation, or the second product (down); float32 sums on the CUDA cores (the float32 path, and
+//                 operands the tensor-core product refuses)
+//   moe_gather    for the tensor-core path: the rows (times their weights) sorted by expert into tiles of 128, every
+//                 expert's rows starting on a tile; the grouped product of csrc/gemm_tc.cu then takes the list of the
+//                 tiles' experts from the device
 //   moe_combine   per token: shared expert's output (if any) + its slots' outputs in slot order
 //
 // The weight multiplies the expert's input (mode "input") or its output (mode "output").
@@ -19,26 +23,40 @@ constexpr int MOE_TT = 16;      // rows per tile
 constexpr int MOE_KC = 256;     // input values per pass through shared memory
 
 // ---------------------------------------------------------------------------------------------- route
-// One warp per token.  scoring 0: sigmoid, 1: softmax over all experts.
+// One block per token: the warps share the experts (a warp per dot product, float32 sums in a fixed order), warp 0 then
+// scores and picks.  scoring 0: sigmoid, 1: softmax over all experts.
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr, int* __restrict__ slot_expert,
-                                 float* __restrict__ slot_weight, int n_tokens, int K, int E, int top, int scoring, int renorm) {
-    extern __shared__ float sc[];   // [warps][E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+__global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr,
+                                                        int* __restrict__ slot_expert, float* __restrict__ slot_weight, int K, int E,
+                                                        int top, int scoring, int renorm) {
+    extern __shared__ float sm[];   // [K] the row in float32, [E] scores
+    float* xs = sm;
+    float* s = sm + K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const size_t t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    if (t >= n_tokens) return;
-    float* s = sc + (size_t)warp * E;
-    const T* x = h + (size_t)t * ldh;
-    for (int e = 0; e < E; ++e) {
+    const T* x = h + t * ldh;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(x[k]);
+    __syncthreads();
+    const bool vec = (K & 3) == 0;
+    for (int e = warp; e < E; e += nwarps) {
         const float* w = wr + (size_t)e * K;
         float acc = 0.f;
-        for (int k = lane; k < K; k += 32) acc = fmaf(to_float(x[k]), w[k], acc);
+        if (vec) {
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 a = *reinterpret_cast<const float4*>(xs + k);
+                const float4 b = __ldg(reinterpret_cast<const float4*>(w + k));
+                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], w[k], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) s[e] = acc;
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     if (scoring == 1) {
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
@@ -68,14 +86,14 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long long ldh, const f
         if (arg >= E) { arg = c < E ? c : 0; best = 0.f; }     // nothing comparable was left: a padded row's garbage
         total += best;
         if (lane == 0) {
-            slot_expert[(size_t)t * top + c] = arg;
-            slot_weight[(size_t)t * top + c] = best;
+            slot_expert[t * top + c] = arg;
+            slot_weight[t * top + c] = best;
             s[arg] = -INFINITY;
         }
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int c = 0; c < top; ++c) slot_weight[(size_t)t * top + c] /= total;
+        for (int c = 0; c < top; ++c) slot_weight[t * top + c] /= total;
 }
 
 LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, int* slot_expert, float* slot_weight, int n_tokens,
@@ -83,19 +101,20 @@ LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, in
     if (n_tokens <= 0) return LLMK_OK;
     if (E <= 0 || top <= 0 || top > E || K <= 0) LLMK_FAIL("moe_route: bad sizes (experts %d, top %d, width %d)", E, top, K);
     if (scoring != 0 && scoring != 1) LLMK_FAIL("moe_route: unknown scoring %d", scoring);
-    const int warps = 4;
-    const size_t smem = (size_t)warps * E * sizeof(float);
-    if (smem > 48 * 1024) LLMK_FAIL("moe_route: %d experts are too many", E);
-    dim3 grid(ceil_div(n_tokens, warps));
+    const size_t smem = ((size_t)K + E) * sizeof(float);
+    if (smem > 200 * 1024) LLMK_FAIL("moe_route: a row of %d values and %d experts do not fit shared memory", K, E);
+    const int threads = E >= 8 ? 256 : 32 * E;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (dtype == LLMK_F32)
-        e = llmk_launch(moe_route_kernel<float>, grid, dim3(warps * 32), smem, s, true, (const float*)h, ldh, wr, slot_expert, slot_weight,
-                        n_tokens, K, E, top, scoring, renorm);
-    else if (dtype == LLMK_BF16)
-        e = llmk_launch(moe_route_kernel<bf16>, grid, dim3(warps * 32), smem, s, true, (const bf16*)h, ldh, wr, slot_expert, slot_weight,
-                        n_tokens, K, E, top, scoring, renorm);
-    else
+    if (dtype == LLMK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, true, (const float*)h, ldh, wr, slot_expert,
+                        slot_weight, K, E, top, scoring, renorm);
+    } else if (dtype == LLMK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(moe_route_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, s, true, (const bf16*)h, ldh, wr, slot_expert,
+                        slot_weight, K, E, top, scoring, renorm);
+    } else
         LLMK_FAIL("moe_route: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("moe_route", e);
     return LLMK_OK;
@@ -104,9 +123,11 @@ LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, in
 // ----------------------------------------------------------------------------------------------- plan
 // order[pos] = slot, pos_of_slot[slot] = pos, slots of one expert side by side (in no particular order: every row
 // is computed by itself).  tile_expert[i], tile_start[i], tile_rows[i] for i < max_tiles; expert -1 pads.
-__global__ void moe_plan_kernel(const int* __restrict__ slot_expert, int n_slots, int E, int max_tiles, int* __restrict__ order,
-                                int* __restrict__ pos_of_slot, int* __restrict__ tile_expert, int* __restrict__ tile_start,
-                                int* __restrict__ tile_rows) {
+// `padded`: every expert's rows begin on a multiple of `tt` (whole tiles per expert, for the grouped tensor-core product);
+// order[pos] is then -1 where a tile has no row.
+__global__ void moe_plan_kernel(const int* __restrict__ slot_expert, int n_slots, int E, int max_tiles, int tt, int padded,
+                                int* __restrict__ order, int* __restrict__ pos_of_slot, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_start, int* __restrict__ tile_rows) {
     extern __shared__ int sh[];     // counts [E], offsets [E], cursors [E]
     int* count = sh;
     int* offset = sh + E;
@@ -125,12 +146,12 @@ __global__ void moe_plan_kernel(const int* __restrict__ slot_expert, int n_slots
         for (int e = 0; e < E; ++e) {
             offset[e] = at;
             cursor[e] = at;
-            for (int r = 0; r < count[e] && tile < max_tiles; r += MOE_TT, ++tile) {
+            for (int r = 0; r < count[e] && tile < max_tiles; r += tt, ++tile) {
                 tile_expert[tile] = e;
                 tile_start[tile] = at + r;
-                tile_rows[tile] = min(MOE_TT, count[e] - r);
+                tile_rows[tile] = min(tt, count[e] - r);
             }
-            at += count[e];
+            at += padded ? ceil_div(count[e], tt) * tt : count[e];
         }
         for (; tile < max_tiles; ++tile) {
             tile_expert[tile] = -1;
@@ -138,6 +159,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ slot_expert, int n_slots
             tile_rows[tile] = 0;
         }
     }
+    if (padded)
+        for (int i = threadIdx.x; i < max_tiles * tt; i += blockDim.x) order[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
         const int e = slot_expert[i];
@@ -151,15 +174,58 @@ __global__ void moe_plan_kernel(const int* __restrict__ slot_expert, int n_slots
     }
 }
 
-LLMK_EXPORT int llmk_moe_max_tiles(int n_slots, int E) { return ceil_div(n_slots, MOE_TT) + E; }
+// The most tiles of `tile` rows (0: this module's own 16) that `n_slots` rows in `E` groups can need.
+LLMK_EXPORT int llmk_moe_max_tiles(int n_slots, int E, int tile) {
+    const int tt = tile > 0 ? tile : MOE_TT;
+    // a group's last tile is partial: at most min(E, n_slots) of them
+    return n_slots / tt + (E < n_slots ? E : n_slots);
+}
 
-LLMK_EXPORT int llmk_moe_plan(const int* slot_expert, int n_slots, int E, int* order, int* pos_of_slot, int* tile_expert,
-                              int* tile_start, int* tile_rows, void* stream) {
+// tile: rows per tile (0: 16, what `moe_experts` takes); padded != 0: experts' rows start on tile boundaries and `order`
+// has max_tiles * tile entries.
+LLMK_EXPORT int llmk_moe_plan(const int* slot_expert, int n_slots, int E, int tile, int padded, int* order, int* pos_of_slot,
+                              int* tile_expert, int* tile_start, int* tile_rows, void* stream) {
     if (n_slots <= 0) return LLMK_OK;
+    const int tt = tile > 0 ? tile : MOE_TT;
     const size_t smem = (size_t)3 * E * sizeof(int);
     if (smem > 48 * 1024) LLMK_FAIL("moe_plan: %d experts are too many", E);
-    LLMK_CHECK_LAUNCH_RC("moe_plan", llmk_launch(moe_plan_kernel, dim3(1), dim3(512), smem, (cudaStream_t)stream, true, slot_expert, n_slots, E,
-                                                 llmk_moe_max_tiles(n_slots, E), order, pos_of_slot, tile_expert, tile_start, tile_rows));
+    LLMK_CHECK_LAUNCH_RC("moe_plan", llmk_launch(moe_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, true, slot_expert, n_slots, E,
+                                                 llmk_moe_max_tiles(n_slots, E, tile), tt, padded, order, pos_of_slot, tile_expert, tile_start,
+                                                 tile_rows));
+    return LLMK_OK;
+}
+
+// --------------------------------------------------------------------------------------------- gather
+// xs[pos, :] = (T)(weight * h[token of order[pos], :]) for the rows a padded plan filled; rows of padding are zeroed.
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, long long ldh, const int* __restrict__ order,
+                                  const float* __restrict__ slot_weight, int top, int K, int scale_rows) {
+    const size_t pos = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = order[pos];
+    T* dst = xs + pos * K;
+    if (slot < 0) {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_float<T>(0.f);
+        return;
+    }
+    const float w = scale_rows ? slot_weight[slot] : 1.f;
+    const T* src = h + (size_t)(slot / top) * ldh;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_float<T>(to_float(src[k]) * w);
+}
+
+LLMK_EXPORT int llmk_moe_gather(void* xs, const void* h, long long ldh, const int* order, const float* slot_weight, int n_rows, int top,
+                                int K, int scale_rows, int dtype, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(moe_gather_kernel<float>, dim3(n_rows), dim3(128), 0, s, true, (float*)xs, (const float*)h, ldh, order, slot_weight, top, K, scale_rows);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(moe_gather_kernel<bf16>, dim3(n_rows), dim3(128), 0, s, true, (bf16*)xs, (const bf16*)h, ldh, order, slot_weight, top, K, scale_rows);
+    else
+        LLMK_FAIL("moe_gather: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("moe_gather", e);
     return LLMK_OK;
 }
 
@@ -255,7 +321,7 @@ LLMK_EXPORT int llmk_moe_experts(float* out, const void* in, long long ld_in, co
                                  int n_slots, int E, int top, int K, int N, int first, int weight_on_input, float alpha, float limit,
                                  int dtype, void* stream) {
     if (n_slots <= 0) return LLMK_OK;
-    dim3 grid(llmk_moe_max_tiles(n_slots, E), ceil_div(N, 128));
+    dim3 grid(llmk_moe_max_tiles(n_slots, E, 0), ceil_div(N, 128));
     cudaStream_t s = (cudaStream_t)stream;
     const int scale_rows = first ? (weight_on_input ? 1 : 0) : (weight_on_input ? 0 : 1);
     cudaError_t e;

@@ -347,12 +347,25 @@ def _cost_moe_experts(a, info: PassInfo) -> Tuple[int, int]:
     return 2 * slots * N * K * both, touched * N * K * both * a["w0"].element_size() + slots * (N + K) * 4
 
 
+def _cost_norm_add(a, info: PassInfo) -> Tuple[int, int]:
+    resid = a["resid"]
+    return 5 * resid.numel(), 2 * _nbytes(resid) + _nbytes(a["y"]) + _nbytes(a["copy"]) + _nbytes(a["weight"])
+
+
+def _cost_grouped_product(a, info: PassInfo) -> Tuple[int, int]:
+    G, N, K = (int(v) for v in a["w"].shape)
+    rows = int(a.get("real_rows") or a["a"].shape[0])
+    touched = min(G, rows)
+    return 2 * rows * N * K, touched * N * K * a["w"].element_size() + rows * (K * a["a"].element_size() + N * a["out"].element_size())
+
+
 # kernel bindings of `ops` that launch work, and how each one's FLOPs and bytes are counted
 OP_COSTS: Dict[str, Callable] = {
-    "norm_add": _cost_all_operands, "cast_rows": _cost_all_operands, "act_rows": _cost_all_operands,
+    "norm_add": _cost_norm_add, "cast_rows": _cost_all_operands, "act_rows": _cost_all_operands,
     "gated_rmsnorm": _cost_all_operands, "linear_attention": _cost_linear_attention, "latent_prep": _cost_latent_prep,
     "latent_absorb": _cost_latent_absorb, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
     "moe_route": _cost_moe_route, "moe_experts": _cost_moe_experts, "moe_combine": _cost_all_operands,
+    "moe_gather": _cost_all_operands, "gemm_tc_grouped": _cost_grouped_product,
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,
     "attn_prep": _cost_attn_prep, "gemm_simt": _cost_product, "gemv_bf16": _cost_product, "gemm_tc": _cost_product,
     "gemm_skinny": _cost_product, "gemm_rows8": _cost_product, "gemm_rows8_gated": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,

@@ -819,8 +819,12 @@ def latent_expand(out: torch.Tensor, oa: torch.Tensor, wuv: torch.Tensor, gate: 
 ROUTER_SCORINGS = {"sigmoid": 0, "softmax": 1}
 
 
-def moe_max_tiles(n_slots: int, experts: int) -> int:
-    return int(build.load("moe").llmk_moe_max_tiles(c_int(n_slots), c_int(experts)))
+MOE_GROUPED_TILE = 128      # rows per tile of the grouped tensor-core product
+
+
+def moe_max_tiles(n_slots: int, experts: int, tile: int = 0) -> int:
+    """The most tiles of `tile` rows (0: the 16 of `moe_experts`) that `n_slots` rows grouped by expert can need."""
+    return int(build.load("moe").llmk_moe_max_tiles(c_int(n_slots), c_int(experts), c_int(tile)))
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, slot_expert: torch.Tensor, slot_weight: torch.Tensor, top: int,
@@ -838,10 +842,41 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, slot_expert: torch.Tensor, 
 
 
 def moe_plan(slot_expert: torch.Tensor, n_slots: int, experts: int, order: torch.Tensor, pos_of_slot: torch.Tensor,
-             tile_expert: torch.Tensor, tile_start: torch.Tensor, tile_rows: torch.Tensor) -> None:
+             tile_expert: torch.Tensor, tile_start: torch.Tensor, tile_rows: torch.Tensor, tile: int = 0, padded: bool = False) -> None:
+    """Groups the slots by expert into tiles of `tile` rows (0: 16).  `padded`: every expert's rows start on a tile, `order`
+    has moe_max_tiles(...) * tile entries (-1 where a tile has no row) and tile i is rows [i * tile, (i + 1) * tile)."""
     lib = build.load("moe")
-    _check(lib, lib.llmk_moe_plan(_ptr(slot_expert), c_int(n_slots), c_int(experts), _ptr(order), _ptr(pos_of_slot), _ptr(tile_expert),
-                                  _ptr(tile_start), _ptr(tile_rows), _stream()))
+    need = moe_max_tiles(n_slots, experts, tile) * tile if padded else n_slots
+    if order.numel() < need or tile_expert.numel() < moe_max_tiles(n_slots, experts, tile):
+        raise KernelError("moe_plan: arrays too small")
+    _check(lib, lib.llmk_moe_plan(_ptr(slot_expert), c_int(n_slots), c_int(experts), c_int(tile), c_int(1 if padded else 0), _ptr(order),
+                                  _ptr(pos_of_slot), _ptr(tile_expert), _ptr(tile_start), _ptr(tile_rows), _stream()))
+
+
+def moe_gather(out: torch.Tensor, h: torch.Tensor, order: torch.Tensor, slot_weight: torch.Tensor, top: int, scale_rows: bool) -> None:
+    """out[pos] = h[order[pos] // top] (times the slot's weight if `scale_rows`), zeros where order[pos] < 0."""
+    lib = build.load("moe")
+    n, K = out.shape
+    if out.dtype != h.dtype or not out.is_contiguous() or order.numel() < n:
+        raise KernelError("moe_gather: shapes or dtypes do not fit")
+    _check(lib, lib.llmk_moe_gather(_ptr(out), _ptr(h), c_longlong(_row_stride(h)), _ptr(order), _ptr(slot_weight), c_int(n), c_int(top),
+                                    c_int(K), c_int(1 if scale_rows else 0), c_int(dtype_code(out.dtype)), _stream()))
+
+
+def gemm_tc_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, real_rows: int = 0) -> None:
+    """out[m] = a[m] @ w[g]^T where g = tile_group[m // 128] (int32 on the device; -1: the tile is skipped): a [M, K] with
+    M a multiple of 128, w [groups, N, K] contiguous, both bfloat16; out [M, N] bfloat16 or float32 (csrc/gemm_tc.cu).
+    `real_rows`: how many rows hold data (for the profiler's count of the work; the kernel does not read it)."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    G, N, Kw = w.shape
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or Kw != K or not w.is_contiguous() or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_tc_grouped: a{list(a.shape)} w{list(w.shape)} out{list(out.shape)} do not fit")
+    if tile_group.dtype != torch.int32 or tile_group.numel() < M // MOE_GROUPED_TILE:
+        raise KernelError("gemm_tc_grouped: one int32 group per tile of 128 rows")
+    _check(lib, lib.llmk_gemm_tc_grouped(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(a)),
+                                         c_longlong(K), c_longlong(_row_stride(out)), c_int(G), _ptr(tile_group),
+                                         c_int(dtype_code(out.dtype)), _ptr(tc_error_flag(a.device)), c_int(1), _stream()))
 
 
 def moe_experts(out: torch.Tensor, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], order: torch.Tensor,

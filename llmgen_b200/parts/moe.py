@@ -53,11 +53,17 @@ class RoutedMLP(FeedForward):
     read back on the host, so a step holding it is recorded into a CUDA graph like any other.
 
     `moe_route` scores each token in float32 against the float32 router and keeps its `top` experts; `moe_plan` groups
-    the (token, choice) slots by expert into tiles of 16 rows (a list of fixed length, padded); `moe_experts` runs the
-    first product with the clamped gated activation and then the down product tile by tile, each tile reading its
-    expert's matrices (stacked [experts, ...] at load); `moe_combine` adds a token's rows in slot order to the shared
-    expert's output.  The shared expert is two of the framework's own products with the same activation between them.
-    The routed products sum in float32 on the CUDA cores (csrc/moe.cu)."""
+    the (token, choice) slots by expert into tiles (a list of fixed length, padded); `moe_combine` adds a token's rows
+    in slot order to the shared expert's output.  The experts' matrices are stacked [experts, ...] at load.  Between
+    plan and sum:
+
+      bfloat16   tiles of 128 rows, every expert's rows starting on a tile: `moe_gather` copies the rows (times their
+                 weights) into that order, and the grouped tensor-core product (`gemm_tc_grouped`: TMA, tcgen05.mma,
+                 the expert of each tile read from the device) runs gate/up of all experts in one launch, the clamped
+                 gated activation follows row-wise, and a second grouped launch runs down
+      float32    (and operands TMA refuses) tiles of 16 rows through `moe_experts`, float32 sums on the CUDA cores
+
+    The shared expert is two of the framework's own products with the same activation between them."""
 
     step_arrays_follow_shapes = True
 
@@ -89,6 +95,12 @@ class RoutedMLP(FeedForward):
         self.w_gate = stack([e.gate_proj for e in spec.experts])     # [E, F, H]
         self.w_up = stack([e.up_proj for e in spec.experts])         # [E, F, H]
         self.w_down = stack([e.down_proj for e in spec.experts])     # [E, H, F]
+        # the tensor-core path reads gate and up as one matrix per expert, [E, 2F, H]: gate rows, then up rows
+        H = spec.hidden_size
+        self.grouped = dtype == torch.bfloat16 and H % 8 == 0 and self.F % 8 == 0 and spec.weight_on_input
+        if self.grouped:
+            self.w_gate_up = torch.cat([self.w_gate, self.w_up], dim=1).contiguous()
+            self.w_gate = self.w_up = None
         self.shared_gate_up = self.shared_down = None
         if spec.shared is not None:
             self.shared_gate_up = torch.cat([weights.device_tensor(spec.shared.gate_proj, dtype, device, keep=False),
@@ -100,27 +112,40 @@ class RoutedMLP(FeedForward):
         H = self.spec.hidden_size
         slots = tokens * self.top
         shared = tokens * (3 * self.spec.shared.intermediate_size + H) * elem if self.spec.shared is not None else 0
-        return slots * (self.F + H) * 4 + tokens * H * 4 + shared + 16 * (slots + self.E) + 2 * ops.SLICED_PRODUCT_BYTES
+        rows = slots + ops.MOE_GROUPED_TILE * min(self.E, slots) if self.grouped else slots
+        return rows * (3 * self.F + 2 * H) * 4 + tokens * H * 4 + shared + 16 * (rows + self.E) + 2 * ops.SLICED_PRODUCT_BYTES
 
     def forward(self, ctx, x):
         T, H = x.shape
         ws = ctx.workspace
         spec, top = self.spec, self.top
         n_slots = T * top
-        tiles = ops.moe_max_tiles(n_slots, self.E)
-        ints = ws.flat("moe_ints", 3 * n_slots + 3 * tiles, torch.int32)
-        slot_expert, order, pos_of_slot = ints[:n_slots], ints[n_slots:2 * n_slots], ints[2 * n_slots:3 * n_slots]
-        tile_expert, tile_start, tile_rows = (ints[3 * n_slots + i * tiles:3 * n_slots + (i + 1) * tiles] for i in range(3))
+        tile = ops.MOE_GROUPED_TILE if self.grouped else 0
+        tiles = ops.moe_max_tiles(n_slots, self.E, tile)
+        n_rows = tiles * tile if self.grouped else n_slots          # rows of the sorted (and, grouped, padded) order
+        ints = ws.flat("moe_ints", 2 * n_slots + n_rows + 3 * tiles, torch.int32)
+        slot_expert, pos_of_slot, order = ints[:n_slots], ints[n_slots:2 * n_slots], ints[2 * n_slots:2 * n_slots + n_rows]
+        tile_expert, tile_start, tile_rows = (ints[2 * n_slots + n_rows + i * tiles:2 * n_slots + n_rows + (i + 1) * tiles] for i in range(3))
         slot_weight = ws.flat("moe_weights", n_slots, torch.float32)
         ops.moe_route(x, self.router, slot_expert, slot_weight, top, spec.scoring, spec.renormalize)
-        ops.moe_plan(slot_expert, n_slots, self.E, order, pos_of_slot, tile_expert, tile_start, tile_rows)
+        ops.moe_plan(slot_expert, n_slots, self.E, order, pos_of_slot, tile_expert, tile_start, tile_rows, tile=tile, padded=self.grouped)
         first = spec.experts[0]
-        y = ws.buffer("moe_act", n_slots, self.F, torch.float32, capacity_rows=ws.default_rows * top)
-        ops.moe_experts(y, x, self.w_gate, self.w_up, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
-                        first=True, weight_on_input=spec.weight_on_input, alpha=first.alpha, limit=first.limit)
-        rows = ws.buffer("moe_rows", n_slots, H, torch.float32, capacity_rows=ws.default_rows * top)
-        ops.moe_experts(rows, y, self.w_down, None, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
-                        first=False, weight_on_input=spec.weight_on_input)
+        cap = (ws.default_rows * top // 128 + self.E) * 128 if self.grouped else ws.default_rows * top
+        rows = ws.buffer("moe_rows", n_rows, H, torch.float32, capacity_rows=cap)
+        if self.grouped:
+            xs = ws.buffer("moe_in", n_rows, H, self.dtype, capacity_rows=cap)
+            ops.moe_gather(xs, x, order, slot_weight, top, scale_rows=spec.weight_on_input)
+            gate_up = ws.buffer("moe_gate_up", n_rows, 2 * self.F, self.dtype, capacity_rows=cap)
+            ops.gemm_tc_grouped(gate_up, xs, self.w_gate_up, tile_expert, real_rows=n_slots)
+            y = ws.buffer("moe_act", n_rows, self.F, self.dtype, capacity_rows=cap)
+            ops.act_rows(y, gate_up, "clamped_glu", alpha=first.alpha, limit=first.limit)
+            ops.gemm_tc_grouped(rows, y, self.w_down, tile_expert, real_rows=n_slots)
+        else:
+            y = ws.buffer("moe_act", n_rows, self.F, torch.float32, capacity_rows=cap)
+            ops.moe_experts(y, x, self.w_gate, self.w_up, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
+                            first=True, weight_on_input=spec.weight_on_input, alpha=first.alpha, limit=first.limit)
+            ops.moe_experts(rows, y, self.w_down, None, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
+                            first=False, weight_on_input=spec.weight_on_input)
         shared_out = None
         if spec.shared is not None:
             Fs = spec.shared.intermediate_size

@@ -277,7 +277,13 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
     needs = {pf._cost_product: [("w",), ("a", "x"), ("out", "slices")], pf._cost_attention: [("nq",), ("nkv",), ("hd",), ("window",), ("kcache",)],
              pf._cost_attn_prep: [("qkv",), ("nq",), ("nk",), ("hd",), ("rot",), ("kcache",), ("cos",)],
              pf._cost_embed: [("out",), ("table",), ("ids",)], pf._cost_norm: [("out",), ("weight",), ("delta",), ("rows",), ("write_resid",)],
-             pf._cost_all_operands: [("out", "out_ids")]}
+             pf._cost_all_operands: [("out", "out_ids")], pf._cost_norm_add: [("resid",), ("y",), ("copy",), ("weight",)],
+             pf._cost_linear_attention: [("heads",), ("dim",), ("vdim",), ("packed",)],
+             pf._cost_latent_attention: [("heads",), ("rank",), ("rot",), ("cache",)],
+             pf._cost_latent_absorb: [("q",), ("qa",), ("wuk",), ("heads",), ("dim",), ("rank",)],
+             pf._cost_latent_expand: [("out",), ("oa",), ("wuv",), ("heads",), ("rank",), ("vdim",)],
+             pf._cost_latent_prep: [("packed",), ("q_rank",), ("rank",), ("rot",)], pf._cost_moe_route: [("h",), ("router",)],
+             pf._cost_moe_experts: [("w0",), ("n_slots",), ("first",)], pf._cost_grouped_product: [("w",), ("a",), ("out",), ("real_rows",)]}
     for name, cost in pf.OP_COSTS.items():
         params = inspect.signature(getattr(ops, name)).parameters
         for alternatives in needs[cost]:
