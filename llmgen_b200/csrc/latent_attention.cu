@@ -107,7 +107,7 @@ LLMK_EXPORT int llmk_latent_prep(const void* packed, long long ld, int dq_off, i
 constexpr int LT_TT = 16;
 
 template <typename T>
-__global__ void __launch_bounds__(256) latent_absorb_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ wuk,
+__global__ void __launch_bounds__(128) latent_absorb_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ wuk,
                                                             float* __restrict__ qa, const int* __restrict__ positions,
                                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                             int n_tokens, int heads, int dim, int rot, int rank, int pairing) {
@@ -135,11 +135,23 @@ __global__ void __launch_bounds__(256) latent_absorb_kernel(const T* __restrict_
     }
     const int za = rank + rot;
     const T* w = wuk + (size_t)h * dim * rank;
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    // this block's slice of the latent's columns: a thread per column, the loads of W eight rows ahead of their use
+    const int r = blockIdx.z * blockDim.x + threadIdx.x;
+    if (r < rank) {
         float acc[LT_TT];
 #pragma unroll
         for (int i = 0; i < LT_TT; ++i) acc[i] = 0.f;
-        for (int d = 0; d < dim; ++d) {
+        int d = 0;
+        for (; d + 8 <= dim; d += 8) {
+            float wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) wv[u] = to_float(w[(size_t)(d + u) * rank + r]);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int i = 0; i < LT_TT; ++i) acc[i] = fmaf(qn[i * dim + d + u], wv[u], acc[i]);
+        }
+        for (; d < dim; ++d) {
             const float wv = to_float(w[(size_t)d * rank + r]);
 #pragma unroll
             for (int i = 0; i < LT_TT; ++i) acc[i] = fmaf(qn[i * dim + d], wv, acc[i]);
@@ -149,10 +161,11 @@ __global__ void __launch_bounds__(256) latent_absorb_kernel(const T* __restrict_
             if (i < n) qa[((size_t)(t0 + i) * heads + h) * za + r] = acc[i];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < LT_TT * rot; idx += blockDim.x) {
-        const int i = idx / rot, d = idx % rot;
-        if (i < n) qa[((size_t)(t0 + i) * heads + h) * za + rank + d] = qo[idx];
-    }
+    if (blockIdx.z == 0)
+        for (int idx = threadIdx.x; idx < LT_TT * rot; idx += blockDim.x) {
+            const int i = idx / rot, dd = idx % rot;
+            if (i < n) qa[((size_t)(t0 + i) * heads + h) * za + rank + dd] = qo[idx];
+        }
 }
 
 LLMK_EXPORT int llmk_latent_absorb(float* qa, const void* q, long long ldq, const void* wuk, const int* positions,
@@ -162,16 +175,16 @@ LLMK_EXPORT int llmk_latent_absorb(float* qa, const void* q, long long ldq, cons
     if (heads <= 0 || heads > 65535 || dim < 0 || rot < 0 || rot % 2 != 0 || rank <= 0) LLMK_FAIL("latent_absorb: bad sizes");
     if (pairing != LLMK_PAIR_INTERLEAVED && pairing != LLMK_PAIR_HALF_SPLIT) LLMK_FAIL("latent_absorb: unknown rotary pairing %d", pairing);
     const size_t smem = (size_t)LT_TT * (dim + 2 * rot) * sizeof(float);
-    dim3 grid(ceil_div(n_tokens, LT_TT), heads);
+    dim3 grid(ceil_div(n_tokens, LT_TT), heads, ceil_div(rank, 128));
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == LLMK_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_absorb_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, s, true, (const float*)q, ldq, (const float*)wuk, qa, positions,
+        e = llmk_launch(latent_absorb_kernel<float>, grid, dim3(128), smem, s, true, (const float*)q, ldq, (const float*)wuk, qa, positions,
                         cos_t, sin_t, n_tokens, heads, dim, rot, rank, pairing);
     } else if (dtype == LLMK_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_absorb_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, s, true, (const bf16*)q, ldq, (const bf16*)wuk, qa, positions,
+        e = llmk_launch(latent_absorb_kernel<bf16>, grid, dim3(128), smem, s, true, (const bf16*)q, ldq, (const bf16*)wuk, qa, positions,
                         cos_t, sin_t, n_tokens, heads, dim, rot, rank, pairing);
     } else
         LLMK_FAIL("latent_absorb: unknown dtype %d", dtype);
@@ -180,12 +193,15 @@ LLMK_EXPORT int llmk_latent_absorb(float* qa, const void* q, long long ldq, cons
 }
 
 // ----------------------------------------------------------------------------------------- attention
-// One block per (tile of queries of one sequence, chunk of heads, key part): up to 16 rows = bq queries x gc
-// heads, two rows a warp; every tile of 32 cached vectors is read once for all rows of the block.  Sequence s owns
-// query rows [cu_q[s], cu_q[s+1]) and has ctx[s] keys after this step; query j of the portion sits at position
-// ctx - q_len + j and sees keys 0..position.  The step's own vectors were written to the cache before.
+// One block per (tile of queries of one sequence, chunk of heads, key part): up to 32 rows = bq queries x gc
+// heads, four rows a warp; every tile of 32 cached vectors is read once (16-byte loads) for all rows of the block.
+// Sequence s owns query rows [cu_q[s], cu_q[s+1]) and has ctx[s] keys after this step; query j of the portion sits at
+// position ctx - q_len + j and sees keys 0..position.  The step's own vectors were written to the cache before.
+// A lane owns one key of the tile for the scores (the queries come as float4 broadcasts) and 1/32 of the latent's
+// values for the weighted sums.
 constexpr int LT_WARPS = 8;
-constexpr int LT_ROWS = 16;
+constexpr int LT_R = 4;                     // rows a warp
+constexpr int LT_ROWS = LT_WARPS * LT_R;
 constexpr int LT_KT = 32;
 
 struct LatentAttnParams {
@@ -205,10 +221,11 @@ struct LatentAttnParams {
 
 template <typename T, int RL>
 __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentAttnParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int za = p.za, rank = p.rank;
-    float* Qs = smem;                       // [ROWS][za], pre-multiplied by scale
-    float* Zs = Qs + LT_ROWS * za;          // [KT][za + 1]
+    const int zq = (za + 3) & ~3;           // a row of queries starts on 16 bytes
+    float* Qs = smem;                       // [ROWS][zq], pre-multiplied by scale
+    float* Zs = Qs + LT_ROWS * zq;          // [KT][za + 1]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_launch_dependents();
     pdl_wait();
@@ -232,58 +249,98 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
     const T* zc = static_cast<const T*>(p.cache);
     const int* bt = p.block_tables + (size_t)s * p.max_blocks;
     const int rows = p.bq * p.gc;
-    for (int idx = threadIdx.x; idx < LT_ROWS * za; idx += blockDim.x) {
-        const int r = idx / za, d = idx % za;
+    for (int idx = threadIdx.x; idx < LT_ROWS * zq; idx += blockDim.x) {
+        const int r = idx / zq, d = idx % zq;
         const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
         float v = 0.f;
-        if (r < rows && qi < nq_tile && hh < p.heads) v = p.qa[((size_t)(q_beg + q0 + qi) * p.heads + hh) * za + d] * p.scale;
+        if (r < rows && qi < nq_tile && hh < p.heads && d < za) v = p.qa[((size_t)(q_beg + q0 + qi) * p.heads + hh) * za + d] * p.scale;
         Qs[idx] = v;
     }
-    int r_of[2], qi_of[2], head_of[2];
-    bool valid[2];
+    int r_of[LT_R], qi_of[LT_R], head_of[LT_R];
+    bool valid[LT_R];
+    bool any_valid = false;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < LT_R; ++i) {
         r_of[i] = warp + i * LT_WARPS;
         qi_of[i] = r_of[i] / p.gc;
         head_of[i] = chunk * p.gc + r_of[i] % p.gc;
         valid[i] = r_of[i] < rows && qi_of[i] < nq_tile && head_of[i] < p.heads && !padding;
+        any_valid = any_valid || valid[i];
     }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float acc[2][RL];
+    float m[LT_R], l[LT_R];
+    float acc[LT_R][RL];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < LT_R; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
 #pragma unroll
         for (int j = 0; j < RL; ++j) acc[i][j] = 0.f;
+    }
+    constexpr int VN = Vec16<T>::N;
+    const bool vec_fill = za % VN == 0 && aligned16(zc);
+    const int vecs = za / VN;
 
     for (int t0 = k_beg; t0 < k_end; t0 += LT_KT) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < LT_KT * za; idx += blockDim.x) {
-            const int key = idx / za, d = idx % za;
-            const int kpos = t0 + key;
-            float v = 0.f;
-            if (kpos < k_end) {
-                const int page = bt[kpos / p.page_size];
-                v = to_float(zc[((size_t)page * p.page_size + kpos % p.page_size) * za + d]);
+        __syncthreads();                    // the tile before is consumed (and Qs written, the first time)
+        if (vec_fill) {
+            for (int idx = threadIdx.x; idx < LT_KT * vecs; idx += blockDim.x) {
+                const int key = idx / vecs, vec = idx % vecs;
+                const int kpos = t0 + key;
+                float f[VN];
+                if (kpos < k_end) {
+                    const int page = bt[kpos / p.page_size];
+                    Vec16<T> v;
+                    v.raw = *reinterpret_cast<const decltype(v.raw)*>(zc + ((size_t)page * p.page_size + kpos % p.page_size) * za + (size_t)vec * VN);
+                    v.unpack(f);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) f[i] = 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < VN; ++i) Zs[key * (za + 1) + vec * VN + i] = f[i];
             }
-            Zs[key * (za + 1) + d] = v;
+        } else {
+            for (int idx = threadIdx.x; idx < LT_KT * za; idx += blockDim.x) {
+                const int key = idx / za, d = idx % za;
+                const int kpos = t0 + key;
+                float v = 0.f;
+                if (kpos < k_end) {
+                    const int page = bt[kpos / p.page_size];
+                    v = to_float(zc[((size_t)page * p.page_size + kpos % p.page_size) * za + d]);
+                }
+                Zs[key * (za + 1) + d] = v;
+            }
         }
         __syncthreads();
-        if (!valid[0] && !valid[1]) continue;
-        float sc[2] = {0.f, 0.f};
+        if (!any_valid) continue;
+        float sc[LT_R];
+#pragma unroll
+        for (int i = 0; i < LT_R; ++i) sc[i] = 0.f;
         {
             const float* kr = Zs + lane * (za + 1);
-            const float* qa = Qs + r_of[0] * za;
-            const float* qb = Qs + (valid[1] ? r_of[1] : r_of[0]) * za;
-            for (int d = 0; d < za; ++d) {
+            const float4* q4[LT_R];
+#pragma unroll
+            for (int i = 0; i < LT_R; ++i) q4[i] = reinterpret_cast<const float4*>(Qs + r_of[i] * zq);
+            const int d4_end = za / 4;
+            for (int d4 = 0; d4 < d4_end; ++d4) {
+                const float k0 = kr[4 * d4], k1 = kr[4 * d4 + 1], k2 = kr[4 * d4 + 2], k3 = kr[4 * d4 + 3];
+#pragma unroll
+                for (int i = 0; i < LT_R; ++i) {
+                    const float4 q = q4[i][d4];
+                    sc[i] = fmaf(q.x, k0, sc[i]); sc[i] = fmaf(q.y, k1, sc[i]);
+                    sc[i] = fmaf(q.z, k2, sc[i]); sc[i] = fmaf(q.w, k3, sc[i]);
+                }
+            }
+            for (int d = 4 * d4_end; d < za; ++d) {
                 const float kv = kr[d];
-                sc[0] = fmaf(qa[d], kv, sc[0]);
-                sc[1] = fmaf(qb[d], kv, sc[1]);
+#pragma unroll
+                for (int i = 0; i < LT_R; ++i) sc[i] = fmaf(Qs[r_of[i] * zq + d], kv, sc[i]);
             }
         }
         const int kpos = t0 + lane;
-        float pr[2];
+        float pr[LT_R];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < LT_R; ++i) {
             const int qpos = first_pos + qi_of[i];
             const bool ok = valid[i] && kpos < k_end && kpos <= qpos;
             const float sv = ok ? sc[i] : -INFINITY;
@@ -302,22 +359,23 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
         }
         const int kmax = min(LT_KT, k_end - t0);
         for (int k = 0; k < kmax; ++k) {
-            const float p0 = __shfl_sync(0xffffffffu, pr[0], k);
-            const float p1 = __shfl_sync(0xffffffffu, pr[1], k);
+            float pk[LT_R];
+#pragma unroll
+            for (int i = 0; i < LT_R; ++i) pk[i] = __shfl_sync(0xffffffffu, pr[i], k);
             const float* vr = Zs + k * (za + 1);
 #pragma unroll
             for (int j = 0; j < RL; ++j) {
                 const int d = lane + 32 * j;
                 if (d < rank) {
                     const float v = vr[d];
-                    acc[0][j] = fmaf(p0, v, acc[0][j]);
-                    acc[1][j] = fmaf(p1, v, acc[1][j]);
+#pragma unroll
+                    for (int i = 0; i < LT_R; ++i) acc[i][j] = fmaf(pk[i], v, acc[i][j]);
                 }
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < LT_R; ++i) {
         const bool owned = r_of[i] < rows && qi_of[i] < max(nq_tile, 0) && head_of[i] < p.heads;
         if (!owned) continue;
         const size_t tok = (size_t)(q_beg + q0 + qi_of[i]);
@@ -344,28 +402,44 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
     }
 }
 
-// One warp per (token, head): merge the key parts in part order.
-__global__ void latent_reduce_kernel(float* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                     int n_rows, int rank, int num_parts) {
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// One block per (token, head): merge the key parts in part order.  The parts' weights e^(m_p - M) are computed once,
+// then every thread adds up its values of the latent over the parts.
+__global__ void __launch_bounds__(128) latent_reduce_kernel(float* __restrict__ out, const float* __restrict__ part_o,
+                                                            const float* __restrict__ part_ml, int rank, int num_parts) {
+    extern __shared__ float wgt[];     // [num_parts] weights, then 1 / denominator
+    const size_t row = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    if (row >= n_rows) return;
-    const float* ml = part_ml + (size_t)row * num_parts * 2;
-    float M = -INFINITY;
-    for (int pt = 0; pt < num_parts; ++pt)
-        if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
-    float denom = 0.f;
-    for (int pt = 0; pt < num_parts; ++pt)
-        if (ml[2 * pt + 1] > 0.f) denom += expf(ml[2 * pt] - M) * ml[2 * pt + 1];
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    float* o = out + (size_t)row * rank;
-    for (int d = lane; d < rank; d += 32) {
+    const float* ml = part_ml + row * num_parts * 2;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int pt = lane; pt < num_parts; pt += 32)
+            if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
+        M = warp_max(M);
+        float denom = 0.f;
+        for (int pt = lane; pt < num_parts; pt += 32) {
+            const float w = ml[2 * pt + 1] > 0.f ? expf(ml[2 * pt] - M) : 0.f;
+            wgt[pt] = w;
+            denom += w * ml[2 * pt + 1];
+        }
+        // the denominator in part order, so that it does not depend on how the lanes were summed
+        __syncwarp();
+        if (lane == 0) {
+            float d = 0.f;
+            for (int pt = 0; pt < num_parts; ++pt) d += wgt[pt] * ml[2 * pt + 1];
+            wgt[num_parts] = d > 0.f ? 1.0f / d : 0.f;
+        }
+        (void)denom;
+    }
+    __syncthreads();
+    const float inv = wgt[num_parts];
+    const float* po = part_o + row * num_parts * rank;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float v = 0.f;
-        for (int pt = 0; pt < num_parts; ++pt)
-            if (ml[2 * pt + 1] > 0.f) v += expf(ml[2 * pt] - M) * part_o[((size_t)row * num_parts + pt) * rank + d];
-        o[d] = v * inv;
+#pragma unroll 4
+        for (int pt = 0; pt < num_parts; ++pt) v = fmaf(wgt[pt], po[(size_t)pt * rank + d], v);
+        out[row * rank + d] = v * inv;
     }
 }
 
@@ -389,7 +463,7 @@ static int dispatch_latent_attention(const LatentAttnParams& p, dim3 grid, size_
     return launch_latent_attention<T, 16>(p, grid, smem, s);
 }
 
-// Queries per tile for `heads` heads: rows = bq * gc <= 16.
+// Queries per tile for `heads` heads: rows = bq * gc <= 32.
 LLMK_EXPORT int llmk_latent_attention_tile_queries(int heads) {
     if (heads <= 0) return 0;
     const int gc = heads < LT_ROWS ? heads : LT_ROWS;
@@ -413,7 +487,7 @@ LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* c
     p.page_size = page_size; p.num_parts = num_parts; p.scale = scale;
     p.part_o = scratch;
     p.part_ml = num_parts > 1 ? scratch + (size_t)n_tokens * heads * num_parts * rank : nullptr;
-    const size_t smem = ((size_t)LT_ROWS * p.za + (size_t)LT_KT * (p.za + 1)) * sizeof(float);
+    const size_t smem = ((size_t)LT_ROWS * ((p.za + 3) & ~3) + (size_t)LT_KT * (p.za + 1)) * sizeof(float);
     if (smem > 220 * 1024) LLMK_FAIL("latent_attention: cached vectors of %d values do not fit shared memory", p.za);
     dim3 grid(n_tiles, p.chunks, num_parts);
     cudaStream_t s = (cudaStream_t)stream;
@@ -427,20 +501,21 @@ LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* c
     if (rc != LLMK_OK) return rc;
     if (num_parts > 1) {
         const int n_rows = n_tokens * heads;
-        const int warps = 4;
-        LLMK_CHECK_LAUNCH_RC("latent_reduce", llmk_launch(latent_reduce_kernel, dim3(ceil_div(n_rows, warps)), dim3(warps * 32), 0, s, true,
-                                                          out, (const float*)p.part_o, (const float*)p.part_ml, n_rows, rank, num_parts));
+        LLMK_CHECK_LAUNCH_RC("latent_reduce", llmk_launch(latent_reduce_kernel, dim3(n_rows), dim3(128), (size_t)(num_parts + 1) * sizeof(float), s,
+                                                          true, out, (const float*)p.part_o, (const float*)p.part_ml, rank, num_parts));
     }
     return LLMK_OK;
 }
 
 // -------------------------------------------------------------------------------------------- expand
-// Block (tile of TT tokens, head); a warp per output value j of the head: out[t, h * vdim + j] =
-// (wuv[h * vdim + j, :] . oa[t, h, :]) * sigmoid(g[t, h * vdim + j]).
+// Block (tile of TT tokens, head, slice of `cols` output values of the head); a warp per output value j:
+// out[t, h * vdim + j] = (wuv[h * vdim + j, :] . oa[t, h, :]) * sigmoid(g[t, h * vdim + j]).  With few tokens a head's
+// outputs are cut into slices of 32 so that there are blocks for the SMs; with many, one block takes the whole head and
+// reads its rows of oa once.
 template <typename T>
 __global__ void __launch_bounds__(256) latent_expand_kernel(T* __restrict__ out, const float* __restrict__ oa, const T* __restrict__ wuv,
                                                             const T* __restrict__ g, long long ldg, int n_tokens, int heads, int rank,
-                                                            int vdim) {
+                                                            int vdim, int cols) {
     extern __shared__ float os[];   // [TT][rank]
     const int t0 = blockIdx.x * LT_TT, h = blockIdx.y;
     const int n = min(LT_TT, n_tokens - t0);
@@ -452,7 +527,8 @@ __global__ void __launch_bounds__(256) latent_expand_kernel(T* __restrict__ out,
         os[idx] = i < n ? oa[((size_t)(t0 + i) * heads + h) * rank + r] : 0.f;
     }
     __syncthreads();
-    for (int j = warp; j < vdim; j += nwarps) {
+    const int j_end = min(vdim, (int)(blockIdx.z + 1) * cols);
+    for (int j = blockIdx.z * cols + warp; j < j_end; j += nwarps) {
         const T* w = wuv + ((size_t)h * vdim + j) * rank;
         float acc[LT_TT];
 #pragma unroll
@@ -482,17 +558,18 @@ LLMK_EXPORT int llmk_latent_expand(void* out, const float* oa, const void* wuv, 
     if (n_tokens <= 0) return LLMK_OK;
     if (heads <= 0 || heads > 65535 || rank <= 0 || vdim <= 0) LLMK_FAIL("latent_expand: bad sizes");
     const size_t smem = (size_t)LT_TT * rank * sizeof(float);
-    dim3 grid(ceil_div(n_tokens, LT_TT), heads);
+    const int cols = n_tokens <= 4 * LT_TT ? 32 : vdim;
+    dim3 grid(ceil_div(n_tokens, LT_TT), heads, ceil_div(vdim, cols));
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == LLMK_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_expand_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = llmk_launch(latent_expand_kernel<float>, grid, dim3(256), smem, s, true, (float*)out, oa, (const float*)wuv, (const float*)g, ldg,
-                        n_tokens, heads, rank, vdim);
+                        n_tokens, heads, rank, vdim, cols);
     } else if (dtype == LLMK_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_expand_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = llmk_launch(latent_expand_kernel<bf16>, grid, dim3(256), smem, s, true, (bf16*)out, oa, (const bf16*)wuv, (const bf16*)g, ldg,
-                        n_tokens, heads, rank, vdim);
+                        n_tokens, heads, rank, vdim, cols);
     } else
         LLMK_FAIL("latent_expand: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("latent_expand", e);

@@ -40,7 +40,7 @@ struct LinAttnParams {
     int heads, dim, vdim, silu;
 };
 
-__device__ __forceinline__ float la_act(float x, int silu) { return silu ? x / (1.0f + expf(-x)) : x; }
+__device__ __forceinline__ float la_act(float x, int silu) { return silu ? __fdividef(x, 1.0f + __expf(-x)) : x; }
 
 template <typename T, int DPT>
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttnParams p) {
@@ -75,19 +75,51 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
     const T* qb = static_cast<const T*>(p.q) + (size_t)h * D;
     const T* kb = static_cast<const T*>(p.k) + (size_t)h * D;
     const T* vb = static_cast<const T*>(p.v) + (size_t)h * E;
+    constexpr int VN = Vec16<T>::N;
+    const bool vec_ok = D % VN == 0 && p.ld % VN == 0 && aligned16(qb) && aligned16(kb);
     for (int c0 = 0; c0 < n_tok; c0 += LA_C) {
         const int n = min(LA_C, n_tok - c0);
         __syncthreads();                    // the chunk before is consumed, Ss and pw are written
-        for (int idx = threadIdx.x; idx < LA_C * D; idx += blockDim.x) {
-            const int i = idx / D, d = idx % D;
-            float qv = 0.f, kv = 0.f;
-            if (i < n) {
-                const size_t row = (size_t)(t_beg + c0 + i) * p.ld;
-                qv = la_act(to_float(qb[row + d]), p.silu);
-                kv = la_act(to_float(kb[row + d]), p.silu);
+        if (vec_ok) {
+            // 16 bytes of q and of k per thread and turn
+            const int vecs = D / VN;
+            for (int idx = threadIdx.x; idx < LA_C * vecs; idx += blockDim.x) {
+                const int i = idx / vecs, d = (idx % vecs) * VN;
+                float qf[VN], kf[VN];
+                if (i < n) {
+                    const size_t row = (size_t)(t_beg + c0 + i) * p.ld;
+                    Vec16<T> qv, kv;
+                    qv.raw = *reinterpret_cast<const decltype(qv.raw)*>(qb + row + d);
+                    kv.raw = *reinterpret_cast<const decltype(kv.raw)*>(kb + row + d);
+                    qv.unpack(qf);
+                    kv.unpack(kf);
+#pragma unroll
+                    for (int u = 0; u < VN; ++u) {
+                        qf[u] = la_act(qf[u], p.silu);
+                        kf[u] = la_act(kf[u], p.silu);
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < VN; ++u) qf[u] = kf[u] = 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < VN; ++u) {
+                    Qs[i * DP + d + u] = qf[u];
+                    Ks[i * DP + d + u] = kf[u];
+                }
             }
-            Qs[i * DP + d] = qv;
-            Ks[i * DP + d] = kv;
+        } else {
+            for (int idx = threadIdx.x; idx < LA_C * D; idx += blockDim.x) {
+                const int i = idx / D, d = idx % D;
+                float qv = 0.f, kv = 0.f;
+                if (i < n) {
+                    const size_t row = (size_t)(t_beg + c0 + i) * p.ld;
+                    qv = la_act(to_float(qb[row + d]), p.silu);
+                    kv = la_act(to_float(kb[row + d]), p.silu);
+                }
+                Qs[i * DP + d] = qv;
+                Ks[i * DP + d] = kv;
+            }
         }
         for (int idx = threadIdx.x; idx < LA_C * LA_EV; idx += blockDim.x) {
             const int i = idx / LA_EV, ee = idx % LA_EV;

@@ -91,12 +91,13 @@ class LatentAttention(Mixer):
         return tokens * per_token + ops.SLICED_PRODUCT_BYTES
 
     def _parts(self, ctx) -> int:
-        """Key parts of a step of single tokens: enough blocks for the SMs, at least 256 keys a part."""
+        """Key parts of a step of single tokens: two blocks an SM, at least 128 keys a part (four tiles of the kernel), at
+        most 32 parts; every sequence's own keys are cut evenly, so the bound of the step's context class decides."""
         if not ctx.pure_decode:
             return 1
-        blocks = max(1, ctx.n_seqs * ((self.heads + 15) // 16))
+        blocks = max(1, ctx.n_seqs * ((self.heads + 31) // 32))
         longest = max(ctx.max_ctx_bound, ctx.max_ctx, 1)
-        return max(1, min((2 * self.sm_count) // blocks, longest // 256, 32))
+        return max(1, min((2 * self.sm_count) // blocks, longest // 128, 32))
 
     def forward(self, ctx, x, cache: LayerCache):
         T = ctx.n_tokens
