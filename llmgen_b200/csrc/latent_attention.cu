@@ -249,12 +249,37 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
     const T* zc = static_cast<const T*>(p.cache);
     const int* bt = p.block_tables + (size_t)s * p.max_blocks;
     const int rows = p.bq * p.gc;
-    for (int idx = threadIdx.x; idx < LT_ROWS * zq; idx += blockDim.x) {
-        const int r = idx / zq, d = idx % zq;
+    if (p.num_parts > 1 && k_beg >= k_end) {
+        // a key part beyond this sequence's keys: its rows say "nothing seen" and the block leaves at once
+        for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+            const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
+            if (qi < max(nq_tile, 0) && hh < p.heads) {
+                const size_t row = ((size_t)(q_beg + q0 + qi) * p.heads + hh) * p.num_parts + part;
+                p.part_ml[row * 2] = -INFINITY;
+                p.part_ml[row * 2 + 1] = 0.f;
+            }
+        }
+        return;
+    }
+    // the block's queries: a warp per row and turn, the lanes across the row (16 bytes each where rows allow it)
+    const bool q_vec = (za & 3) == 0;
+    for (int r = warp; r < LT_ROWS; r += LT_WARPS) {
         const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
-        float v = 0.f;
-        if (r < rows && qi < nq_tile && hh < p.heads && d < za) v = p.qa[((size_t)(q_beg + q0 + qi) * p.heads + hh) * za + d] * p.scale;
-        Qs[idx] = v;
+        const bool live = r < rows && qi < nq_tile && hh < p.heads;
+        const float* src = p.qa + ((size_t)(q_beg + q0 + (live ? qi : 0)) * p.heads + (live ? hh : 0)) * za;
+        float* dst = Qs + r * zq;
+        if (q_vec) {
+            for (int d4 = lane; d4 < zq / 4; d4 += 32) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) {
+                    v = *reinterpret_cast<const float4*>(src + 4 * d4);
+                    v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
+                }
+                *reinterpret_cast<float4*>(dst + 4 * d4) = v;
+            }
+        } else {
+            for (int d = lane; d < zq; d += 32) dst[d] = (live && d < za) ? src[d] * p.scale : 0.f;
+        }
     }
     int r_of[LT_R], qi_of[LT_R], head_of[LT_R];
     bool valid[LT_R];
@@ -282,33 +307,32 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
 
     for (int t0 = k_beg; t0 < k_end; t0 += LT_KT) {
         __syncthreads();                    // the tile before is consumed (and Qs written, the first time)
-        if (vec_fill) {
-            for (int idx = threadIdx.x; idx < LT_KT * vecs; idx += blockDim.x) {
-                const int key = idx / vecs, vec = idx % vecs;
-                const int kpos = t0 + key;
-                float f[VN];
-                if (kpos < k_end) {
-                    const int page = bt[kpos / p.page_size];
-                    Vec16<T> v;
-                    v.raw = *reinterpret_cast<const decltype(v.raw)*>(zc + ((size_t)page * p.page_size + kpos % p.page_size) * za + (size_t)vec * VN);
-                    v.unpack(f);
-                } else {
+        // the tile's cached vectors: a warp takes keys warp, warp + 8, ...; the page of each is looked up once and the
+        // lanes go across the vector, so the loads of a warp's four keys are in flight together
 #pragma unroll
-                    for (int i = 0; i < VN; ++i) f[i] = 0.f;
-                }
+        for (int kk = 0; kk < LT_KT / LT_WARPS; ++kk) {
+            const int key = warp + kk * LT_WARPS;
+            const int kpos = t0 + key;
+            const bool live = kpos < k_end;
+            const T* src = zc;
+            if (live) src = zc + ((size_t)bt[kpos / p.page_size] * p.page_size + kpos % p.page_size) * za;
+            float* dst = Zs + key * (za + 1);
+            if (vec_fill) {
+                for (int vec = lane; vec < vecs; vec += 32) {
+                    float f[VN];
+                    if (live) {
+                        Vec16<T> v;
+                        v.raw = *reinterpret_cast<const decltype(v.raw)*>(src + (size_t)vec * VN);
+                        v.unpack(f);
+                    } else {
 #pragma unroll
-                for (int i = 0; i < VN; ++i) Zs[key * (za + 1) + vec * VN + i] = f[i];
-            }
-        } else {
-            for (int idx = threadIdx.x; idx < LT_KT * za; idx += blockDim.x) {
-                const int key = idx / za, d = idx % za;
-                const int kpos = t0 + key;
-                float v = 0.f;
-                if (kpos < k_end) {
-                    const int page = bt[kpos / p.page_size];
-                    v = to_float(zc[((size_t)page * p.page_size + kpos % p.page_size) * za + d]);
+                        for (int i = 0; i < VN; ++i) f[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) dst[vec * VN + i] = f[i];
                 }
-                Zs[key * (za + 1) + d] = v;
+            } else {
+                for (int d = lane; d < za; d += 32) dst[d] = live ? to_float(src[d]) : 0.f;
             }
         }
         __syncthreads();
@@ -438,7 +462,8 @@ __global__ void __launch_bounds__(128) latent_reduce_kernel(float* __restrict__ 
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float v = 0.f;
 #pragma unroll 4
-        for (int pt = 0; pt < num_parts; ++pt) v = fmaf(wgt[pt], po[(size_t)pt * rank + d], v);
+        for (int pt = 0; pt < num_parts; ++pt)
+            if (wgt[pt] != 0.f) v = fmaf(wgt[pt], po[(size_t)pt * rank + d], v);     // a part that saw nothing wrote nothing
         out[row * rank + d] = v * inv;
     }
 }

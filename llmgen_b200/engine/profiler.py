@@ -146,10 +146,13 @@ class ModelCost:
     w_elem: int                 # bytes per weight
     kv_elem: int                # bytes per cached value
     complete: bool = True       # False: a part of unknown kind was counted as nothing
+    token_flops: int = 0        # per token, outside matrix products and attention over keys (recurrent mixers)
+    state_bytes: int = 0        # recurrent state per sequence (float32), read and written by every step
 
     @classmethod
     def from_spec(cls, spec, w_elem: int = 2, kv_elem: int = 2) -> "ModelCost":
         n_mm, terms, complete = 0, [], True
+        token_flops = state_bytes = 0
         for item in spec.run_order:
             block = spec.layers[item.layer]
             mixer, ffn = getattr(block, "mixer", None), getattr(block, "ffn", None)
@@ -159,14 +162,32 @@ class ModelCost:
                 if item.writes_cache:                       # an item that reads another's cache projects no k, v
                     n_mm += 2 * mixer.hidden_size * kv_dim
                 terms.append(AttentionTerm(q_dim, kv_dim, int(mixer.window or 0)))
+            elif getattr(mixer, "kind", None) == "linear_attention":
+                kd, vd = mixer.num_heads * mixer.key_dim, mixer.num_heads * mixer.value_dim
+                n_mm += mixer.hidden_size * (2 * kd + (3 if mixer.gate_proj else 2) * vd)
+                token_flops += 4 * mixer.num_heads * mixer.key_dim * mixer.value_dim       # the state's update and its product with q
+                state_bytes += 4 * mixer.num_heads * mixer.key_dim * mixer.value_dim
+            elif getattr(mixer, "kind", None) == "latent_attention":
+                n, za = mixer.num_heads, mixer.kv_rank + mixer.rope_dim
+                n_mm += mixer.hidden_size * (mixer.q_rank + za + (2 if mixer.gate_proj else 1) * n * mixer.value_dim)
+                n_mm += mixer.q_rank * n * (mixer.nope_dim + mixer.rope_dim) + n * mixer.kv_rank * (mixer.nope_dim + mixer.value_dim)
+                # one shared entry of kv_rank + rope_dim values per token; per key and head 2 (za + kv_rank) flops
+                terms.append(AttentionTerm(n * (za + mixer.kv_rank) // 2, (za + 1) // 2, 0))
             elif mixer is not None:
                 complete = False
             if getattr(ffn, "kind", None) == "gated_mlp":
                 n_mm += 3 * ffn.hidden_size * ffn.intermediate_size
+            elif getattr(ffn, "kind", None) == "dense_mlp":
+                n_mm += 2 * ffn.hidden_size * ffn.intermediate_size
+            elif getattr(ffn, "kind", None) == "routed_mlp":
+                # what one token uses: the router, its chosen experts and the shared one
+                n_mm += ffn.hidden_size * (len(ffn.experts) + 3 * ffn.top_k * ffn.experts[0].intermediate_size)
+                if ffn.shared is not None:
+                    n_mm += 3 * ffn.hidden_size * ffn.shared.intermediate_size
             elif ffn is not None:
                 complete = False
         head = spec.hidden_size * spec.vocab_size
-        return cls(n_mm + head, head, tuple(terms), w_elem, kv_elem, complete)
+        return cls(n_mm + head, head, tuple(terms), w_elem, kv_elem, complete, token_flops, state_bytes)
 
     @staticmethod
     def _visible_sum(first_ctx: int, n: int, window: int) -> int:
@@ -185,16 +206,16 @@ class ModelCost:
         """A prompt of p tokens under the causal mask, the output projection on `logits_rows` rows
         (the reference's formula projects every row, src/profiler/metrics.zig:228-230)."""
         attn = sum(4 * t.q_dim * self._visible_sum(1, p, t.window) for t in self.attention)
-        return 2 * (self.n_mm - self.head_params) * p + 2 * self.head_params * logits_rows + attn
+        return 2 * (self.n_mm - self.head_params) * p + 2 * self.head_params * logits_rows + attn + self.token_flops * p
 
     def decode_flops(self, c0: int, n: int) -> int:
         """n steps of one sequence whose context (the new token included) is c0, c0 + 1, ..."""
-        return 2 * self.n_mm * n + sum(4 * t.q_dim * self._visible_sum(c0, n, t.window) for t in self.attention)
+        return (2 * self.n_mm + self.token_flops) * n + sum(4 * t.q_dim * self._visible_sum(c0, n, t.window) for t in self.attention)
 
     def decode_bytes(self, c0: int, n: int) -> int:
         """Every weight once a step, and the keys and values the new token sees."""
         kv = sum(2 * t.kv_dim * self.kv_elem * self._visible_sum(c0, n, t.window) for t in self.attention)
-        return self.n_mm * self.w_elem * n + kv
+        return (self.n_mm * self.w_elem + 2 * self.state_bytes) * n + kv
 
 
 def efficiency_text(metrics: GenMetrics, cost: ModelCost, peak_tflops: Optional[float] = None,

@@ -33,10 +33,23 @@ def _layer_body(spec, item) -> str:
     if getattr(mixer, "kind", None) == "attention":
         reach = f"window {mixer.window}" if mixer.window else "all keys"
         parts.append(f"attention {mixer.num_heads}/{mixer.num_kv_heads} heads x {mixer.head_dim}, {reach}")
+    elif getattr(mixer, "kind", None) == "linear_attention":
+        parts.append(f"linear attention {mixer.num_heads} heads x {mixer.key_dim}/{mixer.value_dim}, a decay per head, "
+                     f"state {_size(4 * mixer.num_heads * mixer.key_dim * mixer.value_dim)} a request")
+    elif getattr(mixer, "kind", None) == "latent_attention":
+        parts.append(f"latent attention {mixer.num_heads} heads x {mixer.nope_dim}+{mixer.rope_dim}/{mixer.value_dim}, "
+                     f"latents {mixer.q_rank}/{mixer.kv_rank}, {mixer.kv_rank + mixer.rope_dim} cached values a token")
     elif mixer is not None:
         parts.append(f"mixer '{getattr(mixer, 'kind', '?')}'")
     if getattr(ffn, "kind", None) == "gated_mlp":
         parts.append(f"gated feed-forward {ffn.intermediate_size} ({ffn.activation})")
+    elif getattr(ffn, "kind", None) == "dense_mlp":
+        parts.append(f"feed-forward {ffn.intermediate_size} ({ffn.activation})")
+    elif getattr(ffn, "kind", None) == "routed_mlp":
+        parts.append(f"top {ffn.top_k} of {len(ffn.experts)} experts x {ffn.experts[0].intermediate_size}"
+                     + (f" + shared {ffn.shared.intermediate_size}" if ffn.shared is not None else ""))
+    elif ffn is None and hasattr(block, "ffn"):
+        parts.append("no feed-forward")
     elif ffn is not None:
         parts.append(f"feed-forward '{getattr(ffn, 'kind', '?')}'")
     if item.cache is None:

@@ -49,6 +49,13 @@ WIDE = config([
     latent(17, 8, 4, 8, 24, 16, 0.3, 50.0, dense(48)),
     lightning(2, 72, 80, (0.99, 0.8), None),
 ], width=48, vocab=61, scale=1.0, eps=1e-6)
+# Sizes that are multiples of nothing much (2 and 6): the products fall back from the TMA-fed kernels, the vector loads
+# of the new kernels to their scalar paths, the routed experts in bfloat16 to the tiles of 16 rows.
+ODD = config([
+    latent(5, 6, 6, 10, 14, 18, 0.4, 77.0, moe(4, 3, 12, 0.5, shared=(10, 0.9))),
+    lightning(1, 12, 20, (0.75,), dense(30)),
+    lightning(3, 10, 6, (1.0, 0.3, 0.9), None),
+], width=36, vocab=50, scale=0.5, eps=1e-4)
 # One latent-attention layer whose weights `plant_needle` rewrites so that one token's query finds one other token's key.
 NEEDLE = config([latent(2, 16, 8, 16, 24, 24, 1.0, 30.0, dense(64))], width=32, vocab=53, scale=2.0)
 NEEDLE_ID, PROBE_ID, FILLER_ID = 5, 9, 11

@@ -10,14 +10,15 @@ DTYPES = ["float32", "bfloat16"]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["MIXED", "WIDE"])
-def test_whole_prompt_matches_the_plain_model(name, dtype):
+@pytest.mark.parametrize("name", ["MIXED", "WIDE", "ODD"])
+def test_whole_prompt_and_portions_match_the_plain_model(name, dtype):
     cfg = getattr(du, name)
     model, tensors = du.build(cfg, seed=3, dtype=dtype)
     ids = du.ids_for(cfg, 75, seed=1)
     want = du.plain_logits(cfg, tensors, ids)
-    got = du.run_in_portions(du.driver(model, dtype), "a", ids, [len(ids)])
-    du.assert_close(got, want, dtype)
+    drv = du.driver(model, dtype)
+    du.assert_close(du.run_in_portions(drv, "a", ids, [len(ids)]), want, dtype)
+    du.assert_close(du.run_in_portions(drv, "a", ids, [33, 2, 1, 17, 1]), want, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
