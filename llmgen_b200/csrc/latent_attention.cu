@@ -426,6 +426,276 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_kernel(LatentA
     }
 }
 
+// ------------------------------------------------------------------------------ attention, tensor cores
+// The same attention for bfloat16 caches whose sizes fit (za a multiple of 16, rank a multiple of 64), on the tensor
+// cores by `mma.sync.m16n8k16` with float32 accumulators:
+//   S = Q Z^T          Q rounded to bfloat16 as it enters shared memory, Z as cached; scores float32
+//   O += P Z[:, :rank] the float32 weights P enter as three bfloat16 terms (p = p1 + p2 + p3, 24 bits of mantissa: every
+//                      product p_i z is exact in float32 and the sum is a float32 sum), so the weights are not rounded
+// A block has 8 warps = 2 groups of 16 rows x 4: for the scores a warp takes its group's rows and 8 of the tile's 32
+// keys; the scores pass through shared memory, every warp of a group then does the group's softmax and takes a
+// quarter of the latent's values for the weighted sums.  Rows, tiles, key parts and the merge are those of the
+// kernel above.
+constexpr int MT_KT = 32;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+// p = t1 + t2 + t3 with bfloat16 terms; returns the packed pairs of two neighbouring weights
+__device__ __forceinline__ void split3(float p0, float p1, uint32_t& w1, uint32_t& w2, uint32_t& w3) {
+    const float a0 = __bfloat162float(__float2bfloat16_rn(p0)), a1 = __bfloat162float(__float2bfloat16_rn(p1));
+    const float r0 = p0 - a0, r1 = p1 - a1;
+    const float b0 = __bfloat162float(__float2bfloat16_rn(r0)), b1 = __bfloat162float(__float2bfloat16_rn(r1));
+    w1 = pack_bf16(a0, a1);
+    w2 = pack_bf16(b0, b1);
+    w3 = pack_bf16(r0 - b0, r1 - b1);
+}
+
+template <int NT>       // most tiles of 8 latent values a warp accumulates (rank / 32 of them are used)
+__global__ void __launch_bounds__(256) latent_attention_mma_kernel(LatentAttnParams p) {
+    extern __shared__ __align__(16) unsigned char smem_mma[];
+    const int za = p.za, rank = p.rank;
+    const int zp = za + 8;                                  // row stride: consecutive rows 16 bytes apart in the banks
+    bf16* Qs = reinterpret_cast<bf16*>(smem_mma);            // [32][zp]
+    bf16* Zs = Qs + LT_ROWS * zp;                            // [32][zp]
+    float* Ss = reinterpret_cast<float*>(Zs + MT_KT * zp);   // [32][33]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rg = warp >> 2, wq = warp & 3;                 // group of 16 rows, quarter
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = p.tile_seq[blockIdx.x];
+    if (s < 0) return;
+    const int q0 = p.tile_q0[blockIdx.x];
+    const int chunk = blockIdx.y, part = blockIdx.z;
+    const int q_beg = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - q_beg;
+    const int ctx = p.ctx_len[s];
+    const int nq_tile = min(p.bq, q_len - q0);
+    const bool padding = ctx < q_len || nq_tile <= 0;
+    const int first_pos = ctx - q_len + q0;
+    int k_beg = 0, k_end = 0;
+    if (!padding) k_end = first_pos + nq_tile;
+    if (p.num_parts > 1) {
+        const int part_size = ceil_div(ceil_div(max(ctx, 1), p.num_parts), MT_KT) * MT_KT;
+        k_beg = max(k_beg, part * part_size);
+        k_end = min(k_end, (part + 1) * part_size);
+    }
+    const int rows = p.bq * p.gc;
+    if (p.num_parts > 1 && k_beg >= k_end) {
+        for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+            const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
+            if (qi < max(nq_tile, 0) && hh < p.heads) {
+                const size_t row = ((size_t)(q_beg + q0 + qi) * p.heads + hh) * p.num_parts + part;
+                p.part_ml[row * 2] = -INFINITY;
+                p.part_ml[row * 2 + 1] = 0.f;
+            }
+        }
+        return;
+    }
+    const bf16* zc = static_cast<const bf16*>(p.cache);
+    const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+    // the block's queries, rounded to bfloat16
+    for (int r = warp; r < LT_ROWS; r += LT_WARPS) {
+        const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
+        const bool live = r < rows && qi < nq_tile && hh < p.heads;
+        const float* src = p.qa + ((size_t)(q_beg + q0 + (live ? qi : 0)) * p.heads + (live ? hh : 0)) * za;
+        for (int d = lane * 2; d < za; d += 64) {
+            float2 v = make_float2(0.f, 0.f);
+            if (live) v = *reinterpret_cast<const float2*>(src + d);
+            *reinterpret_cast<__nv_bfloat162*>(Qs + r * zp + d) = __floats2bfloat162_rn(v.x, v.y);
+        }
+    }
+    // this lane's two rows of its group: g and g + 8
+    int qpos[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        const int qi = r / p.gc, hh = chunk * p.gc + r % p.gc;
+        valid[i] = r < rows && qi < nq_tile && hh < p.heads && !padding;
+        qpos[i] = first_pos + qi;
+    }
+    const bool group_live = rg * 16 < rows && (rg * 16) / p.gc < nq_tile;      // uniform over the warp
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+    const int nt = rank / 32;                    // tiles of 8 values this warp accumulates
+    const int d0 = wq * nt * 8;
+    const int vecs = za / 8;
+    const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
+    const uint32_t zs_addr = (uint32_t)__cvta_generic_to_shared(Zs);
+
+    for (int t0 = k_beg; t0 < k_end; t0 += MT_KT) {
+        __syncthreads();                         // the tile before is consumed (and Qs written, the first time)
+#pragma unroll
+        for (int kk = 0; kk < MT_KT / LT_WARPS; ++kk) {
+            const int key = warp + kk * LT_WARPS;
+            const int kpos = t0 + key;
+            const bool live = kpos < k_end;
+            const bf16* src = zc;
+            if (live) src = zc + ((size_t)bt[kpos / p.page_size] * p.page_size + kpos % p.page_size) * za;
+            for (int vec = lane; vec < vecs; vec += 32) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (live) v = *reinterpret_cast<const uint4*>(src + (size_t)vec * 8);
+                *reinterpret_cast<uint4*>(Zs + key * zp + vec * 8) = v;
+            }
+        }
+        __syncthreads();
+        // scores of the group's 16 rows with keys 8 wq .. 8 wq + 7
+        if (group_live) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t a_base = qs_addr + (uint32_t)(((rg * 16 + (lane & 15)) * zp + (lane >> 4) * 8) * 2);
+            const uint32_t b_base = zs_addr + (uint32_t)(((wq * 8 + (lane & 7)) * zp + ((lane >> 3) & 1) * 8) * 2);
+            for (int ks = 0; ks < za / 16; ++ks) {
+                uint32_t a[4], b[2];
+                ldmatrix_x4(a, a_base + (uint32_t)(ks * 32));
+                ldmatrix_x2(b, b_base + (uint32_t)(ks * 32));
+                mma_bf16(c, a, b[0], b[1]);
+            }
+            float* srow = Ss + (rg * 16 + (lane >> 2)) * 33 + wq * 8 + (lane & 3) * 2;
+            srow[0] = c[0] * p.scale;
+            srow[1] = c[1] * p.scale;
+            srow[8 * 33] = c[2] * p.scale;
+            srow[8 * 33 + 1] = c[3] * p.scale;
+        }
+        __syncthreads();
+        if (!group_live) continue;
+        // the group's softmax (every warp of the group does it) in the layout of the next product's first operand
+        float pv[2][2][2][2];                    // [row i][step of 16 keys t][half h][e]
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = 16 * t + 8 * h + (lane & 3) * 2 + e;
+                        const int kpos = t0 + col;
+                        const bool ok = valid[i] && kpos < k_end && kpos <= qpos[i];
+                        const float sv = ok ? Ss[(rg * 16 + (lane >> 2) + 8 * i) * 33 + col] : -INFINITY;
+                        pv[i][t][h][e] = sv;
+                        tmax[i] = fmaxf(tmax[i], sv);
+                    }
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+            const float m_new = fmaxf(m[i], tmax[i]);
+            corr[i] = 1.f;
+            float sum = 0.f;
+            if (m_new > -INFINITY) {
+                corr[i] = m[i] > -INFINITY ? expf(m[i] - m_new) : 0.f;
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float sv = pv[i][t][h][e];
+                            const float pe = sv > -INFINITY ? expf(sv - m_new) : 0.f;
+                            pv[i][t][h][e] = pe;
+                            sum += pe;
+                        }
+                m[i] = m_new;
+            } else {
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) pv[i][t][h][e] = 0.f;
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l[i] = l[i] * corr[i] + sum;
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            acc[j][0] *= corr[0]; acc[j][1] *= corr[0];
+            acc[j][2] *= corr[1]; acc[j][3] *= corr[1];
+        }
+        // weights as three bfloat16 terms, per step of 16 keys: a0 (row g, keys 0-7), a1 (row g + 8), a2 (row g, keys 8-15), a3
+        uint32_t pa[2][3][4];
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    split3(pv[i][t][h][0], pv[i][t][h][1], pa[t][0][2 * h + i], pa[t][1][2 * h + i], pa[t][2][2 * h + i]);
+        // weighted sums over this warp's quarter of the latent's values
+        const uint32_t v_base = zs_addr + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * zp + d0 + (lane >> 4) * 8) * 2);
+#pragma unroll
+        for (int jp = 0; jp < NT / 2; ++jp) {
+            if (2 * jp >= nt) break;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, v_base + (uint32_t)((t * 16 * zp + jp * 16) * 2));
+#pragma unroll
+                for (int term = 0; term < 3; ++term) {
+                    mma_bf16(acc[2 * jp], pa[t][term], b[0], b[1]);
+                    mma_bf16(acc[2 * jp + 1], pa[t][term], b[2], b[3]);
+                }
+            }
+        }
+    }
+    if (!group_live) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        if (!(r < rows && r / p.gc < max(nq_tile, 0) && chunk * p.gc + r % p.gc < p.heads)) continue;     // nobody's row
+        const size_t tokhead = (size_t)(q_beg + q0 + r / p.gc) * p.heads + chunk * p.gc + r % p.gc;
+        if (p.num_parts > 1) {
+            const size_t row = tokhead * p.num_parts + part;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                if (j >= nt) break;
+                const int d = d0 + j * 8 + (lane & 3) * 2;
+                p.part_o[row * rank + d] = acc[j][2 * i];
+                p.part_o[row * rank + d + 1] = acc[j][2 * i + 1];
+            }
+            if (wq == 0 && (lane & 3) == 0) {
+                p.part_ml[row * 2] = m[i];
+                p.part_ml[row * 2 + 1] = l[i];
+            }
+        } else {
+            const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+            float* o = p.out + tokhead * rank;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                if (j >= nt) break;
+                const int d = d0 + j * 8 + (lane & 3) * 2;
+                o[d] = acc[j][2 * i] * inv;
+                o[d + 1] = acc[j][2 * i + 1] * inv;
+            }
+        }
+    }
+}
+
 // One block per (token, head): merge the key parts in part order.  The parts' weights e^(m_p - M) are computed once,
 // then every thread adds up its values of the latent over the parts.
 __global__ void __launch_bounds__(128) latent_reduce_kernel(float* __restrict__ out, const float* __restrict__ part_o,
@@ -488,6 +758,19 @@ static int dispatch_latent_attention(const LatentAttnParams& p, dim3 grid, size_
     return launch_latent_attention<T, 16>(p, grid, smem, s);
 }
 
+template <int NT>
+static int launch_latent_attention_mma(const LatentAttnParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LLMK_FAIL("latent_attention: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+    }
+    LLMK_CHECK_LAUNCH_RC("latent_attention", llmk_launch(latent_attention_mma_kernel<NT>, grid, dim3(LT_WARPS * 32), smem, s, true, p));
+    return LLMK_OK;
+}
+
+static int g_latent_mma = 1;     // 0: the float32 kernel for bfloat16 caches too (for measurements and tests)
+LLMK_EXPORT void llmk_latent_attention_set_mma(int on) { g_latent_mma = on; }
+
 // Queries per tile for `heads` heads: rows = bq * gc <= 32.
 LLMK_EXPORT int llmk_latent_attention_tile_queries(int heads) {
     if (heads <= 0) return 0;
@@ -517,7 +800,16 @@ LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* c
     dim3 grid(n_tiles, p.chunks, num_parts);
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (dtype == LLMK_F32)
+    const bool mma = dtype == LLMK_BF16 && g_latent_mma && p.za % 16 == 0 && rank % 64 == 0 && host_aligned16(cache) &&
+                     ((uintptr_t)qa & 7) == 0;
+    if (mma) {
+        const size_t smem_mma = ((size_t)(LT_ROWS + MT_KT) * (p.za + 8)) * sizeof(bf16) + (size_t)LT_ROWS * 33 * sizeof(float);
+        const int nt = rank / 32;
+        rc = nt <= 2 ? launch_latent_attention_mma<2>(p, grid, smem_mma, s)
+             : nt <= 4 ? launch_latent_attention_mma<4>(p, grid, smem_mma, s)
+             : nt <= 8 ? launch_latent_attention_mma<8>(p, grid, smem_mma, s)
+                       : launch_latent_attention_mma<16>(p, grid, smem_mma, s);
+    } else if (dtype == LLMK_F32)
         rc = dispatch_latent_attention<float>(p, grid, smem, s);
     else if (dtype == LLMK_BF16)
         rc = dispatch_latent_attention<bf16>(p, grid, smem, s);

@@ -778,6 +778,12 @@ def latent_absorb(qa: torch.Tensor, q: torch.Tensor, wuk: torch.Tensor, position
                                        c_int(dtype_code(q.dtype)), _stream()))
 
 
+def latent_attention_set_mma(on: bool) -> None:
+    """Whether `latent_attention` takes bfloat16 caches whose sizes fit to the tensor cores (the default) or runs its
+    float32 kernel for them too (for measurements and tests)."""
+    build.load("latent_attention").llmk_latent_attention_set_mma(c_int(1 if on else 0))
+
+
 def latent_attention_tile_queries(heads: int) -> int:
     return int(build.load("latent_attention").llmk_latent_attention_tile_queries(c_int(heads)))
 

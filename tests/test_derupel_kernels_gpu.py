@@ -121,13 +121,15 @@ def test_routed_feed_forward_matches_the_plain_one(dtype, top, shared):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,dim,rot,vdim,rank", [(3, 16, 8, 24, 32), (17, 8, 4, 8, 16), (2, 24, 0, 16, 40)])
+@pytest.mark.parametrize("heads,dim,rot,vdim,rank", [(3, 16, 8, 24, 32), (17, 8, 4, 8, 16), (2, 24, 0, 16, 40),
+                                                     (3, 16, 16, 24, 64), (17, 8, 32, 8, 128), (6, 8, 64, 16, 512)])
 def test_latent_attention_kernels_match_the_plain_mixer(heads, dim, rot, vdim, rank, dtype):
     """prep, absorb, attention (whole, and a step of single tokens cut into key parts) and expand, on one sequence whose
     pages lie in shuffled order, against keys and values expanded per head."""
     from llmgen_b200.kernels import ops
     dev, dt = "cuda:0", DT[dtype]
-    T, page, q_rank, eps, scale, base = 77, 16, 24, 1e-5, 0.4, 200.0
+    T, page, q_rank, eps, base = 77, 16, 24, 1e-5, 200.0
+    scale = 0.4 / (rank / 32) ** 0.5          # scores of a few units whatever the latent's width
     za = rank + rot
     w = {"dq": rnd((q_rank, 32), 1, 0.3, dt), "dq.norm": 1 + rnd((q_rank,), 2, 0.2), "uq": rnd((heads * (dim + rot), q_rank), 3, 0.3, dt),
          "dkv": rnd((za, 32), 4, 0.3, dt), "dkv.norm": 1 + rnd((rank,), 5, 0.2), "uk": rnd((heads * dim, rank), 6, 0.3, dt),
@@ -168,3 +170,15 @@ def test_latent_attention_kernels_match_the_plain_mixer(heads, dim, rot, vdim, r
     ops.latent_attention(o1, qa[T - 1:], cache, dev_i(table), 5, dev_i([T]), dev_i([0, 1]), dev_i([0]), dev_i([0]), 1, heads, rank, rot,
                          page, scale, parts, scratch)
     close(o1, oa[T - 1:].cpu(), 1e-5)
+    if dtype == "bfloat16" and (rank + rot) % 16 == 0 and rank % 64 == 0:
+        # these sizes went through the tensor cores: the float32 kernel on the same cache and queries differs only by
+        # the rounding of the queries to bfloat16 (the weights enter the second product as three exact terms)
+        ops.latent_attention_set_mma(False)
+        try:
+            ref = torch.empty_like(oa)
+            ops.latent_attention(ref, qa, cache, dev_i(table), 5, dev_i([T]), dev_i([0, T]), dev_i([0] * len(tiles)), dev_i(tiles), T,
+                                 heads, rank, rot, page, scale)
+        finally:
+            ops.latent_attention_set_mma(True)
+        close(oa, ref.cpu(), 5e-2)             # scores of some tens here: a bfloat16 rounding of q moves a weight by a few per cent
+        assert float((oa - ref).abs().max()) > 0
