@@ -17,6 +17,11 @@
 // column, so slices of vdim are independent.  Thread (e, g) = (lane, warp) keeps S[d, e] for d = g, g + 8, ... in
 // registers and a copy of the block's S in shared memory for the S^T q products.
 //
+// A step of more than 256 tokens cuts every sequence's tokens into segments of 256 that run side by side, each from an
+// empty state; a scan over the segments' end states gives the state before each segment (and the request's new
+// state), and a third launch adds that state's share, lambda^(i+1) S_before^T q_i, to the segment's outputs.  A
+// prompt's chunks then no longer form one chain of dependent steps on a handful of SMs.
+//
 // A sequence whose state slot is negative or that brings no tokens (the padding of a step laid out for replay) is
 // skipped.
 #include "common.cuh"
@@ -38,7 +43,21 @@ struct LinAttnParams {
     const int* cu_q;            // [seqs + 1]
     const int* state_slots;     // [seqs]
     int heads, dim, vdim, silu;
+    // segments > 1: a sequence's tokens are cut into segments of LA_SEG, each run by a block of its own from an
+    // empty state; `seg_state` [segments of all sequences][heads][dim][vdim] receives each segment's end state
+    int segments, n_seqs;
+    float* seg_state;
 };
+
+constexpr int LA_SEG = 256;     // tokens per segment (a multiple of the chunk)
+
+// Index of sequence s's first segment among all segments of the step, and how many it has.
+__device__ __forceinline__ int la_segment_base(const int* cu_q, int s, int& count) {
+    int base = 0;
+    for (int i = 0; i < s; ++i) base += max(1, ceil_div(cu_q[i + 1] - cu_q[i], LA_SEG));
+    count = max(1, ceil_div(cu_q[s + 1] - cu_q[s], LA_SEG));
+    return base;
+}
 
 __device__ __forceinline__ float la_act(float x, int silu) { return silu ? __fdividef(x, 1.0f + __expf(-x)) : x; }
 
@@ -54,7 +73,9 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
     float* Ss = As + LA_C * (LA_C + 1);    // [D][EV]
     float* pw = Ss + D * LA_EV;            // [C + 1] powers of the decay
     const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * LA_EV;
+    const int vsplits = ceil_div(p.vdim, LA_EV);
+    const int s = blockIdx.x, h = blockIdx.y, e0 = ((int)blockIdx.z % vsplits) * LA_EV;
+    const int seg = (int)blockIdx.z / vsplits;
     const int e = e0 + lane;
     const bool e_ok = e < E;
     const float lam = p.decay[h];
@@ -62,14 +83,23 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
     pdl_launch_dependents();
     pdl_wait();
     const int slot = p.state_slots[s];
-    const int t_beg = p.cu_q[s], n_tok = p.cu_q[s + 1] - t_beg;
+    int t_beg = p.cu_q[s], n_tok = p.cu_q[s + 1] - t_beg;
     if (slot < 0 || n_tok <= 0) return;
     float* Sg = p.state + (((size_t)slot * p.heads + h) * D) * E;
+    const bool local = p.segments > 1;      // this block runs one segment from an empty state
+    if (local) {
+        if (seg * LA_SEG >= n_tok) return;
+        int count;
+        const int base = la_segment_base(p.cu_q, s, count);
+        Sg = p.seg_state + (((size_t)(base + seg) * p.heads + h) * D) * E;
+        t_beg += seg * LA_SEG;
+        n_tok = min(LA_SEG, n_tok - seg * LA_SEG);
+    }
     float S[DPT];
 #pragma unroll
     for (int r = 0; r < DPT; ++r) {
         const int d = g + LA_WARPS * r;
-        S[r] = (d < D && e_ok) ? Sg[(size_t)d * E + e] : 0.f;
+        S[r] = (d < D && e_ok && !local) ? Sg[(size_t)d * E + e] : 0.f;
         if (d < D) Ss[d * LA_EV + lane] = S[r];
     }
     const T* qb = static_cast<const T*>(p.q) + (size_t)h * D;
@@ -189,6 +219,89 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
     }
 }
 
+// Scan over a sequence's segments, one block per (sequence, head, 32 value columns), a thread per entries (d, e) of the
+// state: `seg_state[g]` holds segment g's end state from an empty start and receives the state BEFORE segment g;
+// the request's state receives the state after the last one.  S_before(g + 1) = lambda^len(g) S_before(g) + S_local(g).
+__global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(LinAttnParams p) {
+    const int D = p.dim, E = p.vdim;
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int s = blockIdx.x, h = blockIdx.y, e = blockIdx.z * LA_EV + lane;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = p.state_slots[s];
+    const int n_tok = p.cu_q[s + 1] - p.cu_q[s];
+    if (slot < 0 || n_tok <= 0 || e >= E) return;
+    int count;
+    const int base = la_segment_base(p.cu_q, s, count);
+    const float lam = p.decay[h];
+    float* Sg = p.state + (((size_t)slot * p.heads + h) * D) * E;
+    for (int d = g; d < D; d += LA_WARPS) {
+        float S = Sg[(size_t)d * E + e];
+        for (int k = 0; k < count; ++k) {
+            float* loc = p.seg_state + (((size_t)(base + k) * p.heads + h) * D + d) * E + e;
+            const float end_local = *loc;
+            *loc = S;
+            S = fmaf(powf(lam, (float)min(LA_SEG, n_tok - k * LA_SEG)), S, end_local);
+        }
+        Sg[(size_t)d * E + e] = S;
+    }
+}
+
+// The share of the state before a segment in the segment's outputs: out[i, e] += lambda^(i + 1) sum_d q_i[d] S_before[d, e],
+// i counting inside the segment.  One block per (sequence, head, 32 value columns x segment), chunks of 32 tokens.
+template <typename T>
+__global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_carry_kernel(LinAttnParams p) {
+    extern __shared__ float smem[];
+    const int D = p.dim, E = p.vdim;
+    const int DP = D + 1;
+    float* Qs = smem;                      // [C][D + 1]
+    float* Ss = Qs + LA_C * DP;            // [D][EV]
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int vsplits = ceil_div(E, LA_EV);
+    const int s = blockIdx.x, h = blockIdx.y, e0 = ((int)blockIdx.z % vsplits) * LA_EV, seg = (int)blockIdx.z / vsplits;
+    const int e = e0 + lane;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = p.state_slots[s];
+    const int n_all = p.cu_q[s + 1] - p.cu_q[s];
+    if (slot < 0 || n_all <= 0 || seg * LA_SEG >= n_all) return;
+    int count;
+    const int base = la_segment_base(p.cu_q, s, count);
+    const float* Sb = p.seg_state + (((size_t)(base + seg) * p.heads + h) * D) * E;
+    const int t_beg = p.cu_q[s] + seg * LA_SEG, n_tok = min(LA_SEG, n_all - seg * LA_SEG);
+    const float lam = p.decay[h];
+    for (int idx = threadIdx.x; idx < D * LA_EV; idx += blockDim.x) {
+        const int d = idx / LA_EV, ee = idx % LA_EV;
+        Ss[idx] = e0 + ee < E ? Sb[(size_t)d * E + e0 + ee] : 0.f;
+    }
+    const T* qb = static_cast<const T*>(p.q) + (size_t)h * D;
+    for (int c0 = 0; c0 < n_tok; c0 += LA_C) {
+        const int n = min(LA_C, n_tok - c0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < LA_C * D; idx += blockDim.x) {
+            const int i = idx / D, d = idx % D;
+            Qs[i * DP + d] = i < n ? la_act(to_float(qb[(size_t)(t_beg + c0 + i) * p.ld + d]), p.silu) : 0.f;
+        }
+        __syncthreads();
+        float acc[LA_C / LA_WARPS];
+#pragma unroll
+        for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = 0.f;
+        for (int d = 0; d < D; ++d) {
+            const float sv = Ss[d * LA_EV + lane];
+#pragma unroll
+            for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = fmaf(Qs[(g + LA_WARPS * r) * DP + d], sv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < LA_C / LA_WARPS; ++r) {
+            const int i = g + LA_WARPS * r;
+            if (i < n && e < E) {
+                float* o = p.out + (size_t)(t_beg + c0 + i) * ((size_t)p.heads * E) + (size_t)h * E + e;
+                *o = fmaf(powf(lam, (float)(c0 + i + 1)), acc[r], *o);
+            }
+        }
+    }
+}
+
 template <typename T, int DPT>
 static int launch_linear_attention(const LinAttnParams& p, dim3 grid, size_t smem, cudaStream_t s) {
     if (smem > 48 * 1024) {
@@ -210,9 +323,19 @@ static int dispatch_linear_attention(const LinAttnParams& p, dim3 grid, size_t s
 
 // q, k, v: pointers to the first row's q, k and v inside the packed projection (rows `ld` elements apart, heads
 // side by side); out float32 [tokens, heads * vdim]; state float32 [slots, heads, dim, vdim]; decay float32 [heads].
+// Floats of scratch that a step of `n_tokens` tokens in `n_seqs` sequences needs for its segments' states (0: the step
+// runs without segments).
+LLMK_EXPORT long long llmk_linear_attention_scratch_floats(int n_tokens, int n_seqs, int heads, int dim, int vdim) {
+    if (n_tokens <= LA_SEG) return 0;
+    return (long long)(n_tokens / LA_SEG + n_seqs) * heads * dim * vdim;
+}
+
+// n_tokens: rows of `out` (all tokens of the step).  With more than LA_SEG of them a sequence's tokens are cut into
+// segments that run side by side (three launches: segments from an empty state, the scan over their end states, the
+// carried state's share of the outputs) and `seg_state` must hold llmk_linear_attention_scratch_floats(...) floats.
 LLMK_EXPORT int llmk_linear_attention(float* out, const void* q, const void* k, const void* v, long long ld, float* state,
                                       const float* decay, const int* cu_q, const int* state_slots, int n_seqs, int heads,
-                                      int dim, int vdim, int silu, int dtype, void* stream) {
+                                      int dim, int vdim, int silu, int n_tokens, float* seg_state, int dtype, void* stream) {
     if (n_seqs <= 0) return LLMK_OK;
     if (heads <= 0 || dim <= 0 || vdim <= 0) LLMK_FAIL("linear_attention: bad sizes (heads %d, dim %d, vdim %d)", heads, dim, vdim);
     if (dim > 32 * LA_WARPS) LLMK_FAIL("linear_attention: dim %d is more than %d", dim, 32 * LA_WARPS);
@@ -220,10 +343,27 @@ LLMK_EXPORT int llmk_linear_attention(float* out, const void* q, const void* k, 
     LinAttnParams p;
     p.q = q; p.k = k; p.v = v; p.ld = ld; p.out = out; p.state = state; p.decay = decay; p.cu_q = cu_q;
     p.state_slots = state_slots; p.heads = heads; p.dim = dim; p.vdim = vdim; p.silu = silu;
+    p.n_seqs = n_seqs;
+    p.segments = n_tokens > LA_SEG ? ceil_div(n_tokens, LA_SEG) : 1;
+    p.seg_state = seg_state;
+    if (p.segments > 1 && !seg_state) LLMK_FAIL("linear_attention: %d tokens need scratch for the segments' states", n_tokens);
+    if (dtype != LLMK_F32 && dtype != LLMK_BF16) LLMK_FAIL("linear_attention: unknown dtype %d", dtype);
+    const int vsplits = ceil_div(vdim, LA_EV);
+    if ((long long)vsplits * p.segments > 65535) LLMK_FAIL("linear_attention: too many segments");
     const size_t smem = ((size_t)2 * LA_C * (dim + 1) + LA_C * LA_EV + LA_C * (LA_C + 1) + (size_t)dim * LA_EV + LA_C + 1) * sizeof(float);
-    dim3 grid(n_seqs, heads, ceil_div(vdim, LA_EV));
+    dim3 grid(n_seqs, heads, vsplits * p.segments);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == LLMK_F32) return dispatch_linear_attention<float>(p, grid, smem, s);
-    if (dtype == LLMK_BF16) return dispatch_linear_attention<bf16>(p, grid, smem, s);
-    LLMK_FAIL("linear_attention: unknown dtype %d", dtype);
+    const int rc = dtype == LLMK_F32 ? dispatch_linear_attention<float>(p, grid, smem, s) : dispatch_linear_attention<bf16>(p, grid, smem, s);
+    if (rc != LLMK_OK || p.segments == 1) return rc;
+    LLMK_CHECK_LAUNCH_RC("linear_attention_scan", llmk_launch(linear_attention_scan_kernel, dim3(n_seqs, heads, vsplits), dim3(LA_WARPS * 32), 0, s,
+                                                              true, p));
+    const size_t smem_c = ((size_t)LA_C * (dim + 1) + (size_t)dim * LA_EV) * sizeof(float);
+    if (dtype == LLMK_F32) {
+        if (smem_c > 48 * 1024) cudaFuncSetAttribute(linear_attention_carry_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
+        LLMK_CHECK_LAUNCH_RC("linear_attention_carry", llmk_launch(linear_attention_carry_kernel<float>, grid, dim3(LA_WARPS * 32), smem_c, s, true, p));
+    } else {
+        if (smem_c > 48 * 1024) cudaFuncSetAttribute(linear_attention_carry_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
+        LLMK_CHECK_LAUNCH_RC("linear_attention_carry", llmk_launch(linear_attention_carry_kernel<bf16>, grid, dim3(LA_WARPS * 32), smem_c, s, true, p));
+    }
+    return LLMK_OK;
 }

@@ -732,9 +732,16 @@ def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight
 
 
 # ------------------------------------------------------------------------------ linear attention
+def linear_attention_scratch_floats(n_tokens: int, n_seqs: int, heads: int, dim: int, vdim: int) -> int:
+    """float32 values of scratch `linear_attention` needs for a step of this shape (0: none)."""
+    lib = build.load("linear_attention")
+    lib.llmk_linear_attention_scratch_floats.restype = c_longlong
+    return int(lib.llmk_linear_attention_scratch_floats(c_int(n_tokens), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim)))
+
+
 def linear_attention(out: torch.Tensor, packed: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor,
                      decay: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, heads: int, dim: int,
-                     vdim: int, silu: bool = True) -> None:
+                     vdim: int, silu: bool = True, scratch: Optional[torch.Tensor] = None) -> None:
     """The decayed outer-product recurrence over each sequence's new tokens (csrc/linear_attention.cu).  `packed`
     [tokens, >= ...] holds q, k (heads x dim) and v (heads x vdim) at the column offsets given; `state` float32
     [slots, heads, dim, vdim] is read and written at each sequence's slot; out float32 [tokens, heads * vdim]."""
@@ -745,10 +752,15 @@ def linear_attention(out: torch.Tensor, packed: torch.Tensor, q_off: int, k_off:
         raise KernelError(f"linear_attention: state must be [slots, {heads}, {dim}, {vdim}], got {list(state.shape)}")
     es = packed.element_size()
     base = packed.data_ptr()
+    n_tokens = out.shape[0]
+    need = linear_attention_scratch_floats(n_tokens, n_seqs, heads, dim, vdim)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"linear_attention: a step of {n_tokens} tokens needs {need} float32 of scratch")
     _check(lib, lib.llmk_linear_attention(_ptr(out), c_void_p(base + q_off * es), c_void_p(base + k_off * es), c_void_p(base + v_off * es),
                                           c_longlong(_row_stride(packed)), _ptr(state), _ptr(decay), _ptr(cu_q), _ptr(state_slots),
                                           c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_int(1 if silu else 0),
-                                          c_int(dtype_code(packed.dtype)), _stream()))
+                                          c_int(n_tokens), _ptr(scratch if need else None), c_int(dtype_code(packed.dtype)), _stream()),
+           3 if need else 1)
 
 
 # ------------------------------------------------------------------------------ latent attention

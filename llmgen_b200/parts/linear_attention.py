@@ -13,7 +13,7 @@ from .spec import LinearAttentionSpec, WeightDecl
 class LinearAttention(Mixer):
     """One packed projection [q | k | v | gate] -> the decayed outer-product recurrence over each sequence's new tokens,
     reading and writing the request's float32 state [heads, key_dim, value_dim] (csrc/linear_attention.cu: prompts in
-    chunks, a decoded token as a chunk of one) -> RMSNorm over the heads side by side times sigmoid(gate), one kernel
+    chunks, a decoded token as a chunk of one, the tokens of a long step in segments that run side by side) -> RMSNorm over the heads side by side times sigmoid(gate), one kernel
     -> output projection.  q, k and v leave the product in the storage dtype; their activation, the recurrence, the
     norm and the gate are float32.
 
@@ -75,8 +75,10 @@ class LinearAttention(Mixer):
         wide = self.heads * self.vd
         packed = linear(x, self.w_in, ws.buffer("linattn_in", T, self.w_in.shape[0], self.dtype))
         o = ws.buffer("linattn_o", T, wide, torch.float32)
+        need = ops.linear_attention_scratch_floats(T, ctx.n_seqs, self.heads, self.kd, self.vd)
+        scratch = ws.flat("linattn_segments", need, torch.float32) if need else None
         ops.linear_attention(o, packed, 0, self.k_off, self.v_off, cache.state, self.decay, ctx.cu_q, ctx.state_slots,
-                             ctx.n_seqs, self.heads, self.kd, self.vd, silu=self.spec.activation == "silu")
+                             ctx.n_seqs, self.heads, self.kd, self.vd, silu=self.spec.activation == "silu", scratch=scratch)
         y = ws.buffer("linattn_y", T, wide, self.dtype)
         if self.spec.gate_proj:
             ops.gated_rmsnorm(y, o, packed[:, self.g_off:], self.norm_gain, self.norm_eps)

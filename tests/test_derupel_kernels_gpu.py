@@ -19,11 +19,12 @@ def close(got, want, tol):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("lens_first,lens_second", [([37, 1, 64], [1, 30, 3]), ([300, 1, 530], [257, 3, 1])])
 @pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 24), (3, 72, 80), (1, 128, 32)])
-def test_linear_attention_kernel_carries_its_state_between_calls(heads, dim, vdim, dtype):
+def test_linear_attention_kernel_carries_its_state_between_calls(heads, dim, vdim, dtype, lens_first, lens_second):
+    """Three sequences, two steps each, in slots 2, 0, 3; the longer steps are cut into segments that run side by side."""
     from llmgen_b200.kernels import ops
     dev = "cuda:0"
-    lens_first, lens_second = [37, 1, 64], [1, 30, 3]          # three sequences, two steps each, in slots 2, 0, 3
     slots = [2, 0, 3]
     decay = [1.0, 0.9, 0.5][:heads]
     width = heads * (2 * dim + vdim) + 8                        # some columns the kernel must skip
@@ -38,8 +39,11 @@ def test_linear_attention_kernel_carries_its_state_between_calls(heads, dim, vdi
         cu = torch.cat([cu[:2], cu[1:2], cu[2:]])
         sl = torch.tensor([slots[0], -1, slots[1], slots[2]], dtype=torch.int32, device=dev)
         out = torch.full((rows.shape[0], heads * vdim), float("nan"), device=dev)
+        need = ops.linear_attention_scratch_floats(rows.shape[0], 4, heads, dim, vdim)
+        assert (need > 0) == (rows.shape[0] > 256)
+        scratch = torch.full((need,), float("nan"), device=dev) if need else None
         ops.linear_attention(out, rows, 0, heads * dim, 2 * heads * dim, state, torch.tensor(decay, device=dev), cu, sl, 4,
-                             heads, dim, vdim, silu=True)
+                             heads, dim, vdim, silu=True, scratch=scratch)
         at = 0
         for i, n in enumerate(lens):
             outs[i].append(out[at:at + n].cpu())
