@@ -12,6 +12,7 @@
 //   latent_prep      per token: cq = rmsnorm(dq~) * gain (the query's latent, for the product that follows);
 //                    c and the rotated kr written to the token's place in the paged cache
 //   latent_absorb    qa[t, h] = [Wuk_h^T qn | rotate(qr)]                      float32 [tokens, heads, rank + rot]
+//                    (or, with Wuk folded into the query's up-projection at load, one product and `latent_rotate`)
 //   latent_attention causal softmax attention of qa over the cached z; float32 scores, weights and sums
 //                    (+ latent_reduce for key parts, flash-decoding)            float32 [tokens, heads, rank]
 //   latent_expand    out[t, h] = (Wuv_h oa[t, h]) * sigmoid(g[t, h])           storage dtype [tokens, heads * vdim]
@@ -189,6 +190,39 @@ LLMK_EXPORT int llmk_latent_absorb(float* qa, const void* q, long long ldq, cons
     } else
         LLMK_FAIL("latent_absorb: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("latent_absorb", e);
+    return LLMK_OK;
+}
+
+// -------------------------------------------------------------------------------------------- rotate
+// For queries that were projected straight into the latent space (Wuk folded into Wuq when the model was loaded):
+// the rotated part of every head of qa [tokens, heads, rank + rot] is turned in place.  One block per token.
+__global__ void latent_rotate_kernel(float* __restrict__ qa, const int* __restrict__ positions, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, int heads, int rank, int rot, int pairing) {
+    const size_t t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int half = rot / 2;
+    const int pos = positions[t];
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        float* q = qa + (t * heads + h) * (size_t)(rank + rot) + rank;
+        const int a = pairing == LLMK_PAIR_INTERLEAVED ? 2 * i : i;
+        const int b = pairing == LLMK_PAIR_INTERLEAVED ? 2 * i + 1 : i + half;
+        const float u = q[a], v = q[b], c = cs[i], sv = sn[i];
+        q[a] = u * c - v * sv;
+        q[b] = v * c + u * sv;
+    }
+}
+
+LLMK_EXPORT int llmk_latent_rotate(float* qa, const int* positions, const float* cos_t, const float* sin_t, int n_tokens, int heads,
+                                   int rank, int rot, int pairing, void* stream) {
+    if (n_tokens <= 0 || rot <= 0) return LLMK_OK;
+    if (rot % 2 != 0 || heads <= 0 || rank < 0) LLMK_FAIL("latent_rotate: bad sizes");
+    if (pairing != LLMK_PAIR_INTERLEAVED && pairing != LLMK_PAIR_HALF_SPLIT) LLMK_FAIL("latent_rotate: unknown rotary pairing %d", pairing);
+    LLMK_CHECK_LAUNCH_RC("latent_rotate", llmk_launch(latent_rotate_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, true, qa, positions,
+                                                      cos_t, sin_t, heads, rank, rot, pairing));
     return LLMK_OK;
 }
 

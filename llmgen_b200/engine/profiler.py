@@ -170,7 +170,10 @@ class ModelCost:
             elif getattr(mixer, "kind", None) == "latent_attention":
                 n, za = mixer.num_heads, mixer.kv_rank + mixer.rope_dim
                 n_mm += mixer.hidden_size * (mixer.q_rank + za + (2 if mixer.gate_proj else 1) * n * mixer.value_dim)
-                n_mm += mixer.q_rank * n * (mixer.nope_dim + mixer.rope_dim) + n * mixer.kv_rank * (mixer.nope_dim + mixer.value_dim)
+                if getattr(mixer, "absorb_at_load", False):     # the query goes straight into the latent space
+                    n_mm += mixer.q_rank * n * za + n * mixer.kv_rank * mixer.value_dim
+                else:
+                    n_mm += mixer.q_rank * n * (mixer.nope_dim + mixer.rope_dim) + n * mixer.kv_rank * (mixer.nope_dim + mixer.value_dim)
                 # one shared entry of kv_rank + rope_dim values per token; per key and head 2 (za + kv_rank) flops
                 terms.append(AttentionTerm(n * (za + mixer.kv_rank) // 2, (za + 1) // 2, 0))
             elif mixer is not None:
@@ -350,6 +353,11 @@ def _cost_latent_expand(a, info: PassInfo) -> Tuple[int, int]:
     return 2 * n * int(a["heads"]) * int(a["rank"]) * int(a["vdim"]), 2 * _nbytes(a["out"]) + _nbytes(a["oa"]) + _nbytes(a["wuv"])
 
 
+def _cost_latent_rotate(a, info: PassInfo) -> Tuple[int, int]:
+    n = int(a["qa"].shape[0])
+    return 3 * n * int(a["heads"]) * int(a["rot"]), 2 * n * int(a["heads"]) * int(a["rot"]) * 4
+
+
 def _cost_latent_prep(a, info: PassInfo) -> Tuple[int, int]:
     n, elem = int(a["packed"].shape[0]), a["packed"].element_size()
     values = int(a["q_rank"]) + int(a["rank"]) + int(a["rot"])
@@ -384,7 +392,7 @@ def _cost_grouped_product(a, info: PassInfo) -> Tuple[int, int]:
 OP_COSTS: Dict[str, Callable] = {
     "norm_add": _cost_norm_add, "cast_rows": _cost_all_operands, "act_rows": _cost_all_operands,
     "gated_rmsnorm": _cost_all_operands, "linear_attention": _cost_linear_attention, "latent_prep": _cost_latent_prep,
-    "latent_absorb": _cost_latent_absorb, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
+    "latent_absorb": _cost_latent_absorb, "latent_rotate": _cost_latent_rotate, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
     "moe_route": _cost_moe_route, "moe_experts": _cost_moe_experts, "moe_combine": _cost_all_operands,
     "moe_gather": _cost_all_operands, "gemm_tc_grouped": _cost_grouped_product,
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,

@@ -790,6 +790,17 @@ def latent_absorb(qa: torch.Tensor, q: torch.Tensor, wuk: torch.Tensor, position
                                        c_int(dtype_code(q.dtype)), _stream()))
 
 
+def latent_rotate(qa: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], heads: int,
+                  rank: int, rot: int, pairing: str) -> None:
+    """Turns the rotated part of every head of qa (float32 [n, heads * (rank + rot)], contiguous) in place."""
+    lib = build.load("latent_attention")
+    n = qa.shape[0]
+    if qa.dtype != torch.float32 or not qa.is_contiguous() or qa.numel() != n * heads * (rank + rot):
+        raise KernelError("latent_rotate: qa is contiguous float32 [n, heads * (rank + rot)]")
+    _check(lib, lib.llmk_latent_rotate(_ptr(qa), _ptr(positions), _ptr(cos), _ptr(sin), c_int(n), c_int(heads), c_int(rank), c_int(rot),
+                                       c_int(pairing_code(pairing)), _stream()))
+
+
 def latent_attention_set_mma(on: bool) -> None:
     """Whether `latent_attention` takes bfloat16 caches whose sizes fit to the tensor cores (the default) or runs its
     float32 kernel for them too (for measurements and tests)."""

@@ -14,8 +14,9 @@ from .spec import LatentAttentionSpec, WeightDecl
 
 class LatentAttention(Mixer):
     """One packed projection [dq | dkv | gate] -> `latent_prep` (the query latent's norm; the key/value latent's norm,
-    the rotation of the shared key part and the write of [c | rotated part] to the paged cache) -> q = cq Wuq^T ->
-    `latent_absorb` (each head's unrotated query taken through Wuk into the latent space, its rotated part turned) ->
+    the rotation of the shared key part and the write of [c | rotated part] to the paged cache) -> the query in the
+    latent space: one product with Wuk folded into Wuq at load and `latent_rotate` (or, `absorb_at_load=False`,
+    q = cq Wuq^T and `latent_absorb`: each head's unrotated query through Wuk, its rotated part turned) ->
     `latent_attention` over the cached vectors, one shared entry per token for all heads -> `latent_expand` (Wuv per
     head, times sigmoid(gate)) -> output projection.  Keys and values of the context are never expanded: a page holds
     kv_rank + rope_dim values per token whatever the number of heads.
@@ -59,8 +60,18 @@ class LatentAttention(Mixer):
         self.w_in = torch.cat([weights.device_tensor(n, dtype, device, keep=False) for n in names], dim=0).contiguous()
         self.dkv_off = self.q_rank
         self.g_off = self.q_rank + self.kv_rank + self.rope
-        self.w_uq = weights.device_tensor(spec.uq_proj, dtype, device)
-        self.w_uk = weights.device_tensor(spec.uk_proj, dtype, device)
+        self.w_uq = weights.device_tensor(spec.uq_proj, dtype, device, keep=not spec.absorb_at_load)
+        self.w_uk = weights.device_tensor(spec.uk_proj, dtype, device, keep=not spec.absorb_at_load)
+        self.w_qa = None
+        if spec.absorb_at_load:
+            # q' = [Wuk_h^T (Wuq_h,unrotated cq) | Wuq_h,rotated cq] = W_qa cq: the products of the two matrices in
+            # float32, stacked head by head in the layout the attention reads, rounded once to the storage dtype
+            n, d, r = self.heads, self.nope, self.rope
+            uq = self.w_uq.float().view(n, d + r, self.q_rank)
+            uk = self.w_uk.float().view(n, d, self.kv_rank)
+            folded = torch.einsum("hdc,hdq->hcq", uk, uq[:, :d])
+            self.w_qa = torch.cat([folded, uq[:, d:]], dim=1).reshape(n * (self.kv_rank + r), self.q_rank).to(dtype).contiguous()
+            self.w_uq = self.w_uk = None
         self.w_uv = weights.device_tensor(spec.uv_proj, dtype, device)
         self.w_o = weights.device_tensor(spec.o_proj, dtype, device)
         self.q_gain = weights.device_tensor(spec.q_norm.weight, dtype, device)
@@ -109,9 +120,14 @@ class LatentAttention(Mixer):
         cq = ws.buffer("latent_cq", T, self.q_rank, self.dtype)
         ops.latent_prep(packed, 0, self.dkv_off, self.q_rank, self.kv_rank, self.rope, self.q_gain, self.kv_gain, self.eps, cq,
                         cache.k if cache.writes else None, ctx.positions, group.slots, cos, sin, self.pairing)
-        q = linear(cq, self.w_uq, ws.buffer("latent_q", T, n * (self.nope + self.rope), self.dtype))
         qa = ws.buffer("latent_qa", T, n * za, torch.float32)
-        ops.latent_absorb(qa, q, self.w_uk, ctx.positions, cos, sin, n, self.nope, self.rope, self.kv_rank, self.pairing)
+        if self.w_qa is not None:
+            linear(cq, self.w_qa, qa)
+            if self.rope:
+                ops.latent_rotate(qa, ctx.positions, cos, sin, n, self.kv_rank, self.rope, self.pairing)
+        else:
+            q = linear(cq, self.w_uq, ws.buffer("latent_q", T, n * (self.nope + self.rope), self.dtype))
+            ops.latent_absorb(qa, q, self.w_uk, ctx.positions, cos, sin, n, self.nope, self.rope, self.kv_rank, self.pairing)
         oa = ws.buffer("latent_oa", T, n * self.kv_rank, torch.float32)
         name = f"attention_tiles_bq{self.bq}"
         parts = self._parts(ctx)

@@ -145,6 +145,9 @@ class LatentAttentionSpec:
     kv_norm: RMSNormSpec
     position: Optional[RopeSpec] = None
     gate_proj: Optional[str] = None
+    # fold Wuk into the query's up-projection when the model is loaded (one product straight into the latent space
+    # instead of a product and a per-head product); False keeps the two matrices apart
+    absorb_at_load: bool = True
     kind: str = "latent_attention"
 
 

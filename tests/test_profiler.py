@@ -282,7 +282,7 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
              pf._cost_latent_attention: [("heads",), ("rank",), ("rot",), ("cache",)],
              pf._cost_latent_absorb: [("q",), ("qa",), ("wuk",), ("heads",), ("dim",), ("rank",)],
              pf._cost_latent_expand: [("out",), ("oa",), ("wuv",), ("heads",), ("rank",), ("vdim",)],
-             pf._cost_latent_prep: [("packed",), ("q_rank",), ("rank",), ("rot",)], pf._cost_moe_route: [("h",), ("router",)],
+             pf._cost_latent_prep: [("packed",), ("q_rank",), ("rank",), ("rot",)], pf._cost_latent_rotate: [("qa",), ("heads",), ("rot",)], pf._cost_moe_route: [("h",), ("router",)],
              pf._cost_moe_experts: [("w0",), ("n_slots",), ("first",)], pf._cost_grouped_product: [("w",), ("a",), ("out",), ("real_rows",)]}
     for name, cost in pf.OP_COSTS.items():
         params = inspect.signature(getattr(ops, name)).parameters
