@@ -182,3 +182,66 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(eager):
     assert llm.executor.cache.all_free()
     if not eager:
         assert llm.executor.n_graph_steps > 0
+
+
+def test_a_model_folder_through_the_replay_program_and_the_command_line(tmp_path):
+    """A Derupel folder written by the random-weights mode: `bin/trace_run` replays a trace of five requests on four state
+    slots and a pool smaller than their sum (float32 logits against the plain model), and `python -m llmgen_b200 chat`
+    generates the plain model's greedy tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from safetensors.torch import load_file
+
+    from llmgen_b200.engine.api import write_random_model
+    from tests.util import ROOT
+    cfg = du.MIXED
+    folder = write_random_model(str(tmp_path / "model"), cfg, seed=12, sigma=0.1, sigma_norm=0.2)
+    with open(os.path.join(folder, "config.json")) as f:
+        assert json.load(f)["architecture"] == "Derupel"
+    tensors = load_file(os.path.join(folder, "model.safetensors"))
+    lengths = [70, 40, 23, 64, 51]
+    ids = [du.ids_for(cfg, n, 70 + i) for i, n in enumerate(lengths)]
+    want = [du.plain_logits(cfg, tensors, t) for t in ids]
+    # requests 0-3 in portions side by side; 4 comes when 2 has ended and takes its slot and pages
+    steps, pos, live, waiting = [], [0] * 5, [0, 1, 2, 3], [4]
+    portions = [17, 2, 1, 30, 1, 1, 64]
+    k = 0
+    while live:
+        entries, ended = [], []
+        for r in live:
+            n = min(portions[(k + r) % len(portions)], lengths[r] - pos[r])
+            entries.append((r, pos[r], pos[r] + n))
+            pos[r] += n
+            if pos[r] == lengths[r]:
+                ended.append(r)
+        steps.append((entries, ended))
+        live = [r for r in live if r not in ended]
+        if ended and waiting:
+            live.append(waiting.pop(0))
+        k += 1
+    lines = [json.dumps({"step": i, "entries": [{"id": f"r{r}", "tokens": ids[r][lo:hi], "want": list(range(hi - lo))} for r, lo, hi in entries],
+                         "end": [f"r{r}" for r in ended]}) for i, (entries, ended) in enumerate(steps)]
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out_dir,
+                           "--max-tokens", "256"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    for i, (entries, _) in enumerate(steps):
+        got = torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{i}.f32"), dtype="<f4").reshape(-1, cfg["vocab"]))
+        ref = torch.cat([want[r][lo:hi] for r, lo, hi in entries])
+        assert du.relative_error(got, ref) < du.TOL["float32"], i
+    # the command line: greedy generation from a prompt of token ids
+    prompt, new = ids[2][:9], 8
+    seq = list(prompt)
+    for _ in range(new):
+        seq.append(int(du.plain_logits(cfg, tensors, seq)[-1].argmax()))
+    proc = subprocess.run([sys.executable, "-m", "llmgen_b200", "chat", ",".join(map(str, prompt)), str(new), "--model", folder, "--dtype", "float32",
+                           "--max-model-len", "64", "--max-num-seqs", "2", "--max-batched-tokens", "64", "--kv-blocks", "8"],
+                          capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    printed = [l.split() for l in proc.stdout.splitlines() if l.split() and all(t.lstrip("-").isdigit() for t in l.split())]
+    assert printed and [int(t) for t in printed[-1]] == seq[len(prompt):], proc.stdout[-2000:]
