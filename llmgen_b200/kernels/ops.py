@@ -164,8 +164,8 @@ def widen(out: torch.Tensor, src: torch.Tensor) -> None:
 
 # ------------------------------------------------------------------------------ attn_prep
 # Codes of the C ABI (csrc/common.cuh).  "half": pairs (i, i + rot / 2), the reference's pairing
-# (src/backend/cpu/rope.zig:13-45); "interleaved": pairs (2i, 2i + 1), which no kernel here implements yet:
-# a position encoding that names it is refused by the kernel with a message, not rotated wrongly.
+# (src/backend/cpu/rope.zig:13-45); "interleaved": pairs (2i, 2i + 1).  The latent-attention kernels implement both; the
+# grouped-query attention kernels implement "half" and refuse the other with a message, never rotate wrongly.
 ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
 HEAD_NORMS = {"rmsnorm": 0}
 
