@@ -127,7 +127,8 @@ def test_routed_feed_forward_matches_the_plain_one(dtype, top, shared):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dim,rot,vdim,rank", [(3, 16, 8, 24, 32), (17, 8, 4, 8, 16), (2, 24, 0, 16, 40),
                                                      (3, 16, 16, 24, 64), (17, 8, 32, 8, 128), (6, 8, 64, 16, 512),
-                                                     (40, 8, 4, 8, 16), (34, 8, 16, 8, 64)])      # more heads than a block has rows
+                                                     (40, 8, 4, 8, 16), (34, 8, 16, 8, 64),      # more heads than a block has rows
+                                                     (2, 8, 16, 8, 192), (2, 8, 0, 8, 256), (1, 16, 32, 8, 320)])
 def test_latent_attention_kernels_match_the_plain_mixer(heads, dim, rot, vdim, rank, dtype):
     """prep, absorb, attention (whole, and a step of single tokens cut into key parts) and expand, on one sequence whose
     pages lie in shuffled order, against keys and values expanded per head."""
