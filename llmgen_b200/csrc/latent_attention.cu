@@ -581,31 +581,57 @@ __global__ void __launch_bounds__(256) latent_attention_mma_kernel(LatentAttnPar
 
     for (int t0 = k_beg; t0 < k_end; t0 += MT_KT) {
         __syncthreads();                         // the tile before is consumed (and Qs written, the first time)
+        // the tile's cached vectors: a warp takes keys warp, warp + 8, ...; the pages of its four keys are looked up
+        // first, then the lanes go across the vectors, the loads of two keys in flight before their stores
+        {
+            const bf16* src[MT_KT / LT_WARPS];
 #pragma unroll
-        for (int kk = 0; kk < MT_KT / LT_WARPS; ++kk) {
-            const int key = warp + kk * LT_WARPS;
-            const int kpos = t0 + key;
-            const bool live = kpos < k_end;
-            const bf16* src = zc;
-            if (live) src = zc + ((size_t)bt[kpos / p.page_size] * p.page_size + kpos % p.page_size) * za;
-            for (int vec = lane; vec < vecs; vec += 32) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) v = *reinterpret_cast<const uint4*>(src + (size_t)vec * 8);
-                *reinterpret_cast<uint4*>(Zs + key * zp + vec * 8) = v;
+            for (int kk = 0; kk < MT_KT / LT_WARPS; ++kk) {
+                const int kpos = t0 + warp + kk * LT_WARPS;
+                src[kk] = kpos < k_end ? zc + ((size_t)bt[kpos / p.page_size] * p.page_size + kpos % p.page_size) * za : nullptr;
+            }
+#pragma unroll
+            for (int kk = 0; kk < MT_KT / LT_WARPS; kk += 2) {
+                for (int vec = lane; vec < vecs; vec += 32) {
+                    uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
+                    if (src[kk]) v0 = *reinterpret_cast<const uint4*>(src[kk] + (size_t)vec * 8);
+                    if (src[kk + 1]) v1 = *reinterpret_cast<const uint4*>(src[kk + 1] + (size_t)vec * 8);
+                    *reinterpret_cast<uint4*>(Zs + (warp + kk * LT_WARPS) * zp + vec * 8) = v0;
+                    *reinterpret_cast<uint4*>(Zs + (warp + (kk + 1) * LT_WARPS) * zp + vec * 8) = v1;
+                }
             }
         }
         __syncthreads();
         // scores of the group's 16 rows with keys 8 wq .. 8 wq + 7
         if (group_live) {
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            // four accumulators in turn, so that consecutive products do not wait for one another
+            float c4[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c4[u][e] = 0.f;
             const uint32_t a_base = qs_addr + (uint32_t)(((rg * 16 + (lane & 15)) * zp + (lane >> 4) * 8) * 2);
             const uint32_t b_base = zs_addr + (uint32_t)(((wq * 8 + (lane & 7)) * zp + ((lane >> 3) & 1) * 8) * 2);
-            for (int ks = 0; ks < za / 16; ++ks) {
+            const int steps = za / 16;
+            int ks = 0;
+            for (; ks + 4 <= steps; ks += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t a[4], b[2];
+                    ldmatrix_x4(a, a_base + (uint32_t)((ks + u) * 32));
+                    ldmatrix_x2(b, b_base + (uint32_t)((ks + u) * 32));
+                    mma_bf16(c4[u], a, b[0], b[1]);
+                }
+            }
+            for (; ks < steps; ++ks) {
                 uint32_t a[4], b[2];
                 ldmatrix_x4(a, a_base + (uint32_t)(ks * 32));
                 ldmatrix_x2(b, b_base + (uint32_t)(ks * 32));
-                mma_bf16(c, a, b[0], b[1]);
+                mma_bf16(c4[0], a, b[0], b[1]);
             }
+            float c[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) c[e] = (c4[0][e] + c4[1][e]) + (c4[2][e] + c4[3][e]);
             float* srow = Ss + (rg * 16 + (lane >> 2)) * 33 + wq * 8 + (lane & 3) * 2;
             srow[0] = c[0] * p.scale;
             srow[1] = c[1] * p.scale;
