@@ -219,32 +219,40 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
     }
 }
 
-// Scan over a sequence's segments, one block per (sequence, head, 32 value columns), a thread per entries (d, e) of the
-// state: `seg_state[g]` holds segment g's end state from an empty start and receives the state BEFORE segment g;
-// the request's state receives the state after the last one.  S_before(g + 1) = lambda^len(g) S_before(g) + S_local(g).
+// Scan over a sequence's segments, a thread per entry (d, e) of the state: `seg_state[g]` holds segment g's end state
+// from an empty start and receives the state BEFORE segment g; the request's state receives the state after the last
+// one.  S_before(g + 1) = lambda^len(g) S_before(g) + S_local(g).  The segments' values are asked for eight at a time
+// before the chain of multiply-adds that needs them.
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(LinAttnParams p) {
     const int D = p.dim, E = p.vdim;
-    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-    const int s = blockIdx.x, h = blockIdx.y, e = blockIdx.z * LA_EV + lane;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int entry = blockIdx.z * blockDim.x + threadIdx.x;        // d * E + e
     pdl_launch_dependents();
     pdl_wait();
     const int slot = p.state_slots[s];
     const int n_tok = p.cu_q[s + 1] - p.cu_q[s];
-    if (slot < 0 || n_tok <= 0 || e >= E) return;
+    if (slot < 0 || n_tok <= 0 || entry >= D * E) return;
     int count;
     const int base = la_segment_base(p.cu_q, s, count);
     const float lam = p.decay[h];
-    float* Sg = p.state + (((size_t)slot * p.heads + h) * D) * E;
-    for (int d = g; d < D; d += LA_WARPS) {
-        float S = Sg[(size_t)d * E + e];
-        for (int k = 0; k < count; ++k) {
-            float* loc = p.seg_state + (((size_t)(base + k) * p.heads + h) * D + d) * E + e;
-            const float end_local = *loc;
-            *loc = S;
-            S = fmaf(powf(lam, (float)min(LA_SEG, n_tok - k * LA_SEG)), S, end_local);
+    const float full = powf(lam, (float)LA_SEG);
+    float* Sg = p.state + ((size_t)slot * p.heads + h) * D * E + entry;
+    const size_t stride = (size_t)p.heads * D * E;
+    float* loc = p.seg_state + ((size_t)base * p.heads + h) * D * E + entry;
+    float S = *Sg;
+    for (int k0 = 0; k0 < count; k0 += 8) {
+        float end_local[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) end_local[u] = k0 + u < count ? loc[(size_t)(k0 + u) * stride] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (k0 + u >= count) break;
+            loc[(size_t)(k0 + u) * stride] = S;
+            const int len = min(LA_SEG, n_tok - (k0 + u) * LA_SEG);
+            S = fmaf(len == LA_SEG ? full : powf(lam, (float)len), S, end_local[u]);
         }
-        Sg[(size_t)d * E + e] = S;
     }
+    *Sg = S;
 }
 
 // The share of the state before a segment in the segment's outputs: out[i, e] += lambda^(i + 1) sum_d q_i[d] S_before[d, e],
@@ -275,12 +283,34 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_carry_kernel(L
         Ss[idx] = e0 + ee < E ? Sb[(size_t)d * E + e0 + ee] : 0.f;
     }
     const T* qb = static_cast<const T*>(p.q) + (size_t)h * D;
+    constexpr int VN = Vec16<T>::N;
+    const bool vec_ok = D % VN == 0 && p.ld % VN == 0 && aligned16(qb);
     for (int c0 = 0; c0 < n_tok; c0 += LA_C) {
         const int n = min(LA_C, n_tok - c0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < LA_C * D; idx += blockDim.x) {
-            const int i = idx / D, d = idx % D;
-            Qs[i * DP + d] = i < n ? la_act(to_float(qb[(size_t)(t_beg + c0 + i) * p.ld + d]), p.silu) : 0.f;
+        if (vec_ok) {
+            const int vecs = D / VN;
+            for (int idx = threadIdx.x; idx < LA_C * vecs; idx += blockDim.x) {
+                const int i = idx / vecs, d = (idx % vecs) * VN;
+                float qf[VN];
+                if (i < n) {
+                    Vec16<T> qv;
+                    qv.raw = *reinterpret_cast<const decltype(qv.raw)*>(qb + (size_t)(t_beg + c0 + i) * p.ld + d);
+                    qv.unpack(qf);
+#pragma unroll
+                    for (int u = 0; u < VN; ++u) qf[u] = la_act(qf[u], p.silu);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < VN; ++u) qf[u] = 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < VN; ++u) Qs[i * DP + d + u] = qf[u];
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < LA_C * D; idx += blockDim.x) {
+                const int i = idx / D, d = idx % D;
+                Qs[i * DP + d] = i < n ? la_act(to_float(qb[(size_t)(t_beg + c0 + i) * p.ld + d]), p.silu) : 0.f;
+            }
         }
         __syncthreads();
         float acc[LA_C / LA_WARPS];
@@ -355,8 +385,8 @@ LLMK_EXPORT int llmk_linear_attention(float* out, const void* q, const void* k, 
     cudaStream_t s = (cudaStream_t)stream;
     const int rc = dtype == LLMK_F32 ? dispatch_linear_attention<float>(p, grid, smem, s) : dispatch_linear_attention<bf16>(p, grid, smem, s);
     if (rc != LLMK_OK || p.segments == 1) return rc;
-    LLMK_CHECK_LAUNCH_RC("linear_attention_scan", llmk_launch(linear_attention_scan_kernel, dim3(n_seqs, heads, vsplits), dim3(LA_WARPS * 32), 0, s,
-                                                              true, p));
+    LLMK_CHECK_LAUNCH_RC("linear_attention_scan", llmk_launch(linear_attention_scan_kernel, dim3(n_seqs, heads, ceil_div(dim * vdim, LA_WARPS * 32)),
+                                                              dim3(LA_WARPS * 32), 0, s, true, p));
     const size_t smem_c = ((size_t)LA_C * (dim + 1) + (size_t)dim * LA_EV) * sizeof(float);
     if (dtype == LLMK_F32) {
         if (smem_c > 48 * 1024) cudaFuncSetAttribute(linear_attention_carry_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
