@@ -242,6 +242,8 @@ struct LatentAttnParams {
     const float* qa;           // [tokens, heads, za]
     const void* cache;         // [pages, page_size, za]
     float* out;                // [tokens, heads, rank]
+    bf16* out_hm;              // or, if set: bfloat16 [heads, t_pad, rank] (head-major, for the grouped product that follows)
+    int t_pad;
     const int* block_tables;
     const int* ctx_len;
     const int* cu_q;
@@ -744,6 +746,16 @@ __global__ void __launch_bounds__(256) latent_attention_mma_kernel(LatentAttnPar
             }
         } else {
             const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+            if (p.out_hm) {
+                bf16* o = p.out_hm + ((size_t)(chunk * p.gc + r % p.gc) * p.t_pad + (size_t)(q_beg + q0 + r / p.gc)) * rank;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    if (j >= nt) break;
+                    const int d = d0 + j * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<__nv_bfloat162*>(o + d) = __floats2bfloat162_rn(acc[j][2 * i] * inv, acc[j][2 * i + 1] * inv);
+                }
+                continue;
+            }
             float* o = p.out + tokhead * rank;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
@@ -759,7 +771,8 @@ __global__ void __launch_bounds__(256) latent_attention_mma_kernel(LatentAttnPar
 // One block per (token, head): merge the key parts in part order.  The parts' weights e^(m_p - M) are computed once,
 // then every thread adds up its values of the latent over the parts.
 __global__ void __launch_bounds__(128) latent_reduce_kernel(float* __restrict__ out, const float* __restrict__ part_o,
-                                                            const float* __restrict__ part_ml, int rank, int num_parts) {
+                                                            const float* __restrict__ part_ml, int rank, int num_parts,
+                                                            bf16* __restrict__ out_hm, int heads, int t_pad) {
     extern __shared__ float wgt[];     // [num_parts] weights, then 1 / denominator
     const size_t row = blockIdx.x;
     pdl_launch_dependents();
@@ -794,7 +807,8 @@ __global__ void __launch_bounds__(128) latent_reduce_kernel(float* __restrict__ 
 #pragma unroll 4
         for (int pt = 0; pt < num_parts; ++pt)
             if (wgt[pt] != 0.f) v = fmaf(wgt[pt], po[(size_t)pt * rank + d], v);     // a part that saw nothing wrote nothing
-        out[row * rank + d] = v * inv;
+        if (out_hm) out_hm[((row % heads) * t_pad + row / heads) * rank + d] = __float2bfloat16_rn(v * inv);
+        else out[row * rank + d] = v * inv;
     }
 }
 
@@ -838,10 +852,16 @@ LLMK_EXPORT int llmk_latent_attention_tile_queries(int heads) {
     return LT_ROWS / gc;
 }
 
+// 1 if a bfloat16 cache of these sizes goes through the tensor cores (and may then leave its result head-major).
+LLMK_EXPORT int llmk_latent_attention_on_tensor_cores(int rank, int rot, int dtype) {
+    return dtype == LLMK_BF16 && g_latent_mma && (rank + rot) % 16 == 0 && rank % 64 == 0 && rank <= 512;
+}
+
+// out_hm (optional, tensor-core form only): the result as bfloat16 [heads, t_pad, rank] instead of float32 in `out`.
 LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* cache, const int* block_tables, int max_blocks,
                                       const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles,
                                       int n_tokens, int heads, int rank, int rot, int page_size, float scale, int num_parts,
-                                      float* scratch, int dtype, void* stream) {
+                                      float* scratch, void* out_hm, int t_pad, int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     if (heads <= 0 || rank <= 0 || rank > 512 || rot < 0) LLMK_FAIL("latent_attention: bad sizes (heads %d, rank %d, rot %d)", heads, rank, rot);
     if (page_size <= 0) LLMK_FAIL("latent_attention: page_size %d", page_size);
@@ -855,13 +875,15 @@ LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* c
     p.page_size = page_size; p.num_parts = num_parts; p.scale = scale;
     p.part_o = scratch;
     p.part_ml = num_parts > 1 ? scratch + (size_t)n_tokens * heads * num_parts * rank : nullptr;
+    p.out_hm = static_cast<bf16*>(out_hm);
+    p.t_pad = t_pad;
     const size_t smem = ((size_t)LT_ROWS * ((p.za + 3) & ~3) + (size_t)LT_KT * (p.za + 1)) * sizeof(float);
     if (smem > 220 * 1024) LLMK_FAIL("latent_attention: cached vectors of %d values do not fit shared memory", p.za);
     dim3 grid(n_tiles, p.chunks, num_parts);
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    const bool mma = dtype == LLMK_BF16 && g_latent_mma && p.za % 16 == 0 && rank % 64 == 0 && host_aligned16(cache) &&
-                     ((uintptr_t)qa & 7) == 0;
+    const bool mma = llmk_latent_attention_on_tensor_cores(rank, rot, dtype) && host_aligned16(cache) && ((uintptr_t)qa & 7) == 0;
+    if (out_hm && (!mma || t_pad < n_tokens)) LLMK_FAIL("latent_attention: a head-major result needs the tensor-core form and room for %d tokens", n_tokens);
     if (mma) {
         const size_t smem_mma = ((size_t)(LT_ROWS + MT_KT) * (p.za + 8)) * sizeof(bf16) + (size_t)LT_ROWS * 33 * sizeof(float);
         const int nt = rank / 32;
@@ -879,8 +901,47 @@ LLMK_EXPORT int llmk_latent_attention(float* out, const float* qa, const void* c
     if (num_parts > 1) {
         const int n_rows = n_tokens * heads;
         LLMK_CHECK_LAUNCH_RC("latent_reduce", llmk_launch(latent_reduce_kernel, dim3(n_rows), dim3(128), (size_t)(num_parts + 1) * sizeof(float), s,
-                                                          true, out, (const float*)p.part_o, (const float*)p.part_ml, rank, num_parts));
+                                                          true, out, (const float*)p.part_o, (const float*)p.part_ml, rank, num_parts,
+                                                          mma ? p.out_hm : nullptr, heads, p.t_pad));
     }
+    return LLMK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- gate
+// After the grouped product Wuv_h oa_h: out[t, h * vdim + j] = (T)(o[(h * t_pad + t) * vdim + j] * sigmoid(g[t, h * vdim + j])),
+// o float32 head-major.
+template <typename T>
+__global__ void latent_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g, long long ldg, int n_tokens,
+                                   int heads, int vdim, int t_pad) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)n_tokens * heads * vdim;
+    const int wide = heads * vdim;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const size_t t = (size_t)(i / wide);
+        const int c = (int)(i % wide), h = c / vdim, j = c % vdim;
+        float v = o[((size_t)h * t_pad + t) * vdim + j];
+        if (g) v *= 1.0f / (1.0f + expf(-to_float(g[t * ldg + c])));
+        out[i] = from_float<T>(v);
+    }
+}
+
+LLMK_EXPORT int llmk_latent_gate(void* out, const float* o, const void* g, long long ldg, int n_tokens, int heads, int vdim, int t_pad,
+                                 int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    long long blocks = ((long long)n_tokens * heads * vdim + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(latent_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, o, (const float*)g, ldg, n_tokens,
+                        heads, vdim, t_pad);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(latent_gate_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, o, (const bf16*)g, ldg, n_tokens,
+                        heads, vdim, t_pad);
+    else
+        LLMK_FAIL("latent_gate: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("latent_gate", e);
     return LLMK_OK;
 }
 

@@ -392,7 +392,7 @@ def _cost_grouped_product(a, info: PassInfo) -> Tuple[int, int]:
 OP_COSTS: Dict[str, Callable] = {
     "norm_add": _cost_norm_add, "cast_rows": _cost_all_operands, "act_rows": _cost_all_operands,
     "gated_rmsnorm": _cost_all_operands, "linear_attention": _cost_linear_attention, "latent_prep": _cost_latent_prep,
-    "latent_absorb": _cost_latent_absorb, "latent_rotate": _cost_latent_rotate, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
+    "latent_absorb": _cost_latent_absorb, "latent_rotate": _cost_latent_rotate, "latent_gate": _cost_all_operands, "latent_attention": _cost_latent_attention, "latent_expand": _cost_latent_expand,
     "moe_route": _cost_moe_route, "moe_experts": _cost_moe_experts, "moe_combine": _cost_all_operands,
     "moe_gather": _cost_all_operands, "gemm_tc_grouped": _cost_grouped_product,
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,

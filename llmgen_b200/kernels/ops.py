@@ -815,22 +815,46 @@ def latent_attention_scratch_floats(n_tokens: int, heads: int, rank: int, parts:
     return 0 if parts <= 1 else n_tokens * heads * parts * (rank + 2)
 
 
-def latent_attention(out: torch.Tensor, qa: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, max_blocks: int,
+def latent_attention_on_tensor_cores(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """Whether `latent_attention` takes a cache of this dtype and these sizes to the tensor cores."""
+    return bool(build.load("latent_attention").llmk_latent_attention_on_tensor_cores(c_int(rank), c_int(rot), c_int(dtype_code(dtype))))
+
+
+def latent_attention(out: Optional[torch.Tensor], qa: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, max_blocks: int,
                      ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tokens: int,
                      heads: int, rank: int, rot: int, page_size: int, scale: float, parts: int = 1,
-                     scratch: Optional[torch.Tensor] = None) -> None:
+                     scratch: Optional[torch.Tensor] = None, out_head_major: Optional[torch.Tensor] = None) -> None:
     """out float32 [n, heads, rank] = causal softmax attention of qa over the cached vectors (one shared kv head whose
-    values are the first `rank` entries of the cached vector)."""
+    values are the first `rank` entries of the cached vector).  With `out_head_major` (bfloat16 [heads, t_pad, rank]; the
+    tensor-core form only) the result goes there instead, rounded, for the grouped product that follows."""
     lib = build.load("latent_attention")
-    if out.dtype != torch.float32 or qa.dtype != torch.float32:
-        raise KernelError("latent_attention: queries and outputs are float32")
+    t_pad = 0
+    if out_head_major is not None:
+        if out_head_major.dtype != torch.bfloat16 or out_head_major.dim() != 3 or out_head_major.shape[0] != heads \
+                or out_head_major.shape[2] != rank or not out_head_major.is_contiguous():
+            raise KernelError("latent_attention: the head-major result is contiguous bfloat16 [heads, t_pad, rank]")
+        t_pad = out_head_major.shape[1]
+    elif out is None or out.dtype != torch.float32:
+        raise KernelError("latent_attention: outputs are float32")
+    if qa.dtype != torch.float32:
+        raise KernelError("latent_attention: queries are float32")
     if parts > 1 and (scratch is None or scratch.numel() < latent_attention_scratch_floats(n_tokens, heads, rank, parts)):
         raise KernelError("latent_attention: scratch too small")
     _check(lib, lib.llmk_latent_attention(_ptr(out), _ptr(qa), _ptr(cache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len),
                                           _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(tile_seq.numel()), c_int(n_tokens),
                                           c_int(heads), c_int(rank), c_int(rot), c_int(page_size), c_float(scale), c_int(parts),
-                                          _ptr(scratch), c_int(dtype_code(cache.dtype)), _stream()),
+                                          _ptr(scratch), _ptr(out_head_major), c_int(t_pad), c_int(dtype_code(cache.dtype)), _stream()),
            2 if parts > 1 else 1)
+
+
+def latent_gate(out: torch.Tensor, o: torch.Tensor, gate: Optional[torch.Tensor], heads: int, vdim: int, t_pad: int) -> None:
+    """out[n, heads * vdim] (storage dtype) = o (float32 [heads, t_pad, vdim], head-major) * sigmoid(gate)."""
+    lib = build.load("latent_attention")
+    n = out.shape[0]
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.numel() < heads * t_pad * vdim or (gate is not None and gate.dtype != out.dtype):
+        raise KernelError("latent_gate: shapes or dtypes do not fit")
+    _check(lib, lib.llmk_latent_gate(_ptr(out), _ptr(o), _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(n),
+                                     c_int(heads), c_int(vdim), c_int(t_pad), c_int(dtype_code(out.dtype)), _stream()))
 
 
 def latent_expand(out: torch.Tensor, oa: torch.Tensor, wuv: torch.Tensor, gate: Optional[torch.Tensor], heads: int, rank: int,

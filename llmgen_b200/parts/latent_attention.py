@@ -17,8 +17,10 @@ class LatentAttention(Mixer):
     the rotation of the shared key part and the write of [c | rotated part] to the paged cache) -> the query in the
     latent space: one product with Wuk folded into Wuq at load and `latent_rotate` (or, `absorb_at_load=False`,
     q = cq Wuq^T and `latent_absorb`: each head's unrotated query through Wuk, its rotated part turned) ->
-    `latent_attention` over the cached vectors, one shared entry per token for all heads -> `latent_expand` (Wuv per
-    head, times sigmoid(gate)) -> output projection.  Keys and values of the context are never expanded: a page holds
+    `latent_attention` over the cached vectors, one shared entry per token for all heads -> Wuv per head and the gate:
+    in bfloat16 with sizes the tensor-core attention takes, the attention leaves its result head-major in bfloat16, one
+    grouped tcgen05 product (a group per head) applies Wuv and `latent_gate` multiplies by sigmoid(gate); otherwise
+    `latent_expand` does both on the CUDA cores -> output projection.  Keys and values of the context are never expanded: a page holds
     kv_rank + rope_dim values per token whatever the number of heads.
 
     Scores, softmax weights and their sums with the latents are float32 (csrc/latent_attention.cu); a step of single
@@ -81,6 +83,11 @@ class LatentAttention(Mixer):
         self.pairing = getattr(self.position, "pairing", "half") if self.position is not None else "half"
         self.bq = ops.latent_attention_tile_queries(self.heads)
         self.sm_count = ops.sm_count(device)
+        # bfloat16 caches whose sizes fit leave the attention head-major in bfloat16, and Wuv runs as one grouped tensor-core
+        # product over all heads (a group per head); the list of the tiles' heads is made once per padded token count
+        self.grouped_expand = (ops.latent_attention_on_tensor_cores(dtype, self.kv_rank, self.rope) and self.vd % 8 == 0)
+        self._head_of_tile = {}
+        self.device = device
 
     def cache_request(self) -> KVRequest:
         return KVRequest(FULL, 0, 1, self.kv_rank + self.rope, values=False)
@@ -128,17 +135,39 @@ class LatentAttention(Mixer):
         else:
             q = linear(cq, self.w_uq, ws.buffer("latent_q", T, n * (self.nope + self.rope), self.dtype))
             ops.latent_absorb(qa, q, self.w_uk, ctx.positions, cos, sin, n, self.nope, self.rope, self.kv_rank, self.pairing)
-        oa = ws.buffer("latent_oa", T, n * self.kv_rank, torch.float32)
         name = f"attention_tiles_bq{self.bq}"
         parts = self._parts(ctx)
         scratch = None
         if parts > 1:
             scratch = ws.flat("latent_split", ops.latent_attention_scratch_floats(T, n, self.kv_rank, parts), torch.float32)
-        ops.latent_attention(oa, qa, cache.k, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, ctx.array(name + "_seq"),
-                             ctx.array(name + "_q0"), T, n, self.kv_rank, self.rope, cache.page_size, float(self.spec.scale), parts, scratch)
+        gate = packed[:, self.g_off:] if self.spec.gate_proj else None
         y = ws.buffer("latent_y", T, n * self.vd, self.dtype)
-        ops.latent_expand(y, oa, self.w_uv, packed[:, self.g_off:] if self.spec.gate_proj else None, n, self.kv_rank, self.vd)
+        if self.grouped_expand:
+            t_pad = (T + ops.MOE_GROUPED_TILE - 1) // ops.MOE_GROUPED_TILE * ops.MOE_GROUPED_TILE
+            cap = (ws.default_rows + ops.MOE_GROUPED_TILE - 1) // ops.MOE_GROUPED_TILE * ops.MOE_GROUPED_TILE * n
+            oa_hm = ws.buffer("latent_oa_hm", n * t_pad, self.kv_rank, self.dtype, capacity_rows=cap)
+            ops.latent_attention(None, qa, cache.k, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, ctx.array(name + "_seq"),
+                                 ctx.array(name + "_q0"), T, n, self.kv_rank, self.rope, cache.page_size, float(self.spec.scale), parts,
+                                 scratch, out_head_major=oa_hm.view(n, t_pad, self.kv_rank))
+            o_hm = ws.buffer("latent_o_hm", n * t_pad, self.vd, torch.float32, capacity_rows=cap)
+            ops.gemm_tc_grouped(o_hm, oa_hm, self.w_uv.view(n, self.vd, self.kv_rank), self._tile_heads(t_pad), real_rows=n * T)
+            ops.latent_gate(y, o_hm, gate, n, self.vd, t_pad)
+        else:
+            oa = ws.buffer("latent_oa", T, n * self.kv_rank, torch.float32)
+            ops.latent_attention(oa, qa, cache.k, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, ctx.array(name + "_seq"),
+                                 ctx.array(name + "_q0"), T, n, self.kv_rank, self.rope, cache.page_size, float(self.spec.scale), parts,
+                                 scratch)
+            ops.latent_expand(y, oa, self.w_uv, gate, n, self.kv_rank, self.vd)
         return linear_sliced(ws, "mixer_out", y, self.w_o, self.dtype)
+
+    def _tile_heads(self, t_pad: int) -> torch.Tensor:
+        """int32 [heads * t_pad / 128] on the device: the head of every 128-row tile of the head-major rows."""
+        tiles = self._head_of_tile.get(t_pad)
+        if tiles is None:
+            per_head = t_pad // ops.MOE_GROUPED_TILE
+            tiles = torch.arange(self.heads, dtype=torch.int32).repeat_interleave(per_head).to(self.device)
+            self._head_of_tile[t_pad] = tiles
+        return tiles
 
 
 register_mixer("latent_attention", LatentAttention)

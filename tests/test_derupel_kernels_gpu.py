@@ -186,5 +186,15 @@ def test_latent_attention_kernels_match_the_plain_mixer(heads, dim, rot, vdim, r
                                  heads, rank, rot, page, scale)
         finally:
             ops.latent_attention_set_mma(True)
+        # the same result head-major in bfloat16 (what the grouped product over the heads reads), whole and from key parts
+        t_pad = 128
+        hm = torch.zeros(heads, t_pad, rank, dtype=torch.bfloat16, device=dev)
+        ops.latent_attention(None, qa, cache, dev_i(table), 5, dev_i([T]), dev_i([0, T]), dev_i([0] * len(tiles)), dev_i(tiles), T, heads,
+                             rank, rot, page, scale, out_head_major=hm)
+        close(hm[:, :T].permute(1, 0, 2).reshape(T, heads * rank).float(), oa.cpu(), 1e-2)
+        hm1 = torch.zeros(heads, t_pad, rank, dtype=torch.bfloat16, device=dev)
+        ops.latent_attention(None, qa[T - 1:], cache, dev_i(table), 5, dev_i([T]), dev_i([0, 1]), dev_i([0]), dev_i([0]), 1, heads, rank, rot,
+                             page, scale, parts, scratch, out_head_major=hm1)
+        close(hm1[:, 0].reshape(1, heads * rank).float(), oa[T - 1:].cpu(), 1e-2)
         close(oa, ref.cpu(), 5e-2)             # scores of some tens here: a bfloat16 rounding of q moves a weight by a few per cent
         assert float((oa - ref).abs().max()) > 0
