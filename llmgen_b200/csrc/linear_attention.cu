@@ -63,12 +63,14 @@ __device__ __forceinline__ float la_act(float x, int silu) { return silu ? __fdi
 
 template <typename T, int DPT>
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttnParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int D = p.dim, E = p.vdim;
-    const int DP = D + 1;
-    float* Qs = smem;                      // [C][D + 1]
-    float* Ks = Qs + LA_C * DP;            // [C][D + 1]
-    float* Vs = Ks + LA_C * DP;            // [C][EV]
+    const int DP = D + 1;                  // rows of k: a lane per row reads without bank conflicts
+    const int DQ = (D + 3) & ~3;           // rows of q: read as float4 broadcasts
+    float* Qs = smem;                      // [C][DQ]
+    float* Ks = Qs + LA_C * DQ;            // [C][D + 1]
+    float* Kt = Ks + LA_C * DP;            // [D][C]: the keys once more, a key dimension's 32 tokens side by side
+    float* Vs = Kt + D * LA_C;             // [C][EV]
     float* As = Vs + LA_C * LA_EV;         // [C][C + 1]
     float* Ss = As + LA_C * (LA_C + 1);    // [D][EV]
     float* pw = Ss + D * LA_EV;            // [C + 1] powers of the decay
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
                 }
 #pragma unroll
                 for (int u = 0; u < VN; ++u) {
-                    Qs[i * DP + d + u] = qf[u];
+                    Qs[i * DQ + d + u] = qf[u];
                     Ks[i * DP + d + u] = kf[u];
                 }
             }
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
                     qv = la_act(to_float(qb[row + d]), p.silu);
                     kv = la_act(to_float(kb[row + d]), p.silu);
                 }
-                Qs[i * DP + d] = qv;
+                Qs[i * DQ + d] = qv;
                 Ks[i * DP + d] = kv;
             }
         }
@@ -158,16 +160,34 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
             Vs[idx] = vv;
         }
         __syncthreads();
-        // scores: warp g takes rows i = g, g + 8, ...; lane j the key
-        for (int i = g; i < LA_C; i += LA_WARPS) {
-            float a = 0.f;
-            if (lane <= i && i < n) {
-                const float* qi = Qs + i * DP;
-                const float* kj = Ks + lane * DP;
-                for (int d = 0; d < D; ++d) a = fmaf(qi[d], kj[d], a);
-                a *= pw[i - lane];
+        // the keys once more, transposed (read by the state's update, two barriers from here)
+        for (int d = g; d < D; d += LA_WARPS) Kt[d * LA_C + lane] = Ks[lane * DP + d];
+        // scores: warp g takes rows i = g, g + 8, g + 16, g + 24 together, lane j the key; a key value is read once
+        // for the four rows, the queries come as float4 broadcasts
+        {
+            constexpr int R = LA_C / LA_WARPS;
+            float a[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) a[r] = 0.f;
+            const float* kj = Ks + lane * DP;
+            for (int d4 = 0; d4 < D / 4; ++d4) {
+                const float k0 = kj[4 * d4], k1 = kj[4 * d4 + 1], k2 = kj[4 * d4 + 2], k3 = kj[4 * d4 + 3];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float4 q = *reinterpret_cast<const float4*>(Qs + (g + LA_WARPS * r) * DQ + 4 * d4);
+                    a[r] = fmaf(q.x, k0, a[r]); a[r] = fmaf(q.y, k1, a[r]); a[r] = fmaf(q.z, k2, a[r]); a[r] = fmaf(q.w, k3, a[r]);
+                }
             }
-            As[i * (LA_C + 1) + lane] = a;
+            for (int d = D & ~3; d < D; ++d) {
+                const float kv = kj[d];
+#pragma unroll
+                for (int r = 0; r < R; ++r) a[r] = fmaf(Qs[(g + LA_WARPS * r) * DQ + d], kv, a[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int i = g + LA_WARPS * r;
+                As[i * (LA_C + 1) + lane] = (lane <= i && i < n) ? a[r] * pw[i - lane] : 0.f;
+            }
         }
         __syncthreads();
         // outputs: thread (e, g) takes rows i = g, g + 8, g + 16, g + 24
@@ -175,10 +195,19 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
             float acc[LA_C / LA_WARPS];
 #pragma unroll
             for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = 0.f;
-            for (int d = 0; d < D; ++d) {
+            for (int d4 = 0; d4 < D / 4; ++d4) {
+                const float s0 = Ss[(4 * d4) * LA_EV + lane], s1 = Ss[(4 * d4 + 1) * LA_EV + lane];
+                const float s2 = Ss[(4 * d4 + 2) * LA_EV + lane], s3 = Ss[(4 * d4 + 3) * LA_EV + lane];
+#pragma unroll
+                for (int r = 0; r < LA_C / LA_WARPS; ++r) {
+                    const float4 q = *reinterpret_cast<const float4*>(Qs + (g + LA_WARPS * r) * DQ + 4 * d4);
+                    acc[r] = fmaf(q.x, s0, acc[r]); acc[r] = fmaf(q.y, s1, acc[r]); acc[r] = fmaf(q.z, s2, acc[r]); acc[r] = fmaf(q.w, s3, acc[r]);
+                }
+            }
+            for (int d = D & ~3; d < D; ++d) {
                 const float sv = Ss[d * LA_EV + lane];
 #pragma unroll
-                for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = fmaf(Qs[(g + LA_WARPS * r) * DP + d], sv, acc[r]);
+                for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = fmaf(Qs[(g + LA_WARPS * r) * DQ + d], sv, acc[r]);
             }
 #pragma unroll
             for (int r = 0; r < LA_C / LA_WARPS; ++r) {
@@ -196,12 +225,28 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(LinAttn
             float add[DPT];
 #pragma unroll
             for (int r = 0; r < DPT; ++r) add[r] = 0.f;
-            for (int j = 0; j < n; ++j) {
-                const float vj = Vs[j * LA_EV + lane] * pw[n - 1 - j];
+            // sixteen tokens at a time: their decayed values in registers, a key dimension's sixteen tokens as four float4
+            // broadcasts (rows beyond the chunk hold zeros)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float vw[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const int j = 16 * half + u;
+                    vw[u] = j < n ? Vs[j * LA_EV + lane] * pw[n - 1 - j] : 0.f;
+                }
 #pragma unroll
                 for (int r = 0; r < DPT; ++r) {
                     const int d = g + LA_WARPS * r;
-                    if (d < D) add[r] = fmaf(Ks[j * DP + d], vj, add[r]);
+                    if (d < D) {
+                        const float4* kt = reinterpret_cast<const float4*>(Kt + d * LA_C + 16 * half);
+#pragma unroll
+                        for (int u4 = 0; u4 < 4; ++u4) {
+                            const float4 k = kt[u4];
+                            add[r] = fmaf(k.x, vw[4 * u4], add[r]); add[r] = fmaf(k.y, vw[4 * u4 + 1], add[r]);
+                            add[r] = fmaf(k.z, vw[4 * u4 + 2], add[r]); add[r] = fmaf(k.w, vw[4 * u4 + 3], add[r]);
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -380,7 +425,8 @@ LLMK_EXPORT int llmk_linear_attention(float* out, const void* q, const void* k, 
     if (dtype != LLMK_F32 && dtype != LLMK_BF16) LLMK_FAIL("linear_attention: unknown dtype %d", dtype);
     const int vsplits = ceil_div(vdim, LA_EV);
     if ((long long)vsplits * p.segments > 65535) LLMK_FAIL("linear_attention: too many segments");
-    const size_t smem = ((size_t)2 * LA_C * (dim + 1) + LA_C * LA_EV + LA_C * (LA_C + 1) + (size_t)dim * LA_EV + LA_C + 1) * sizeof(float);
+    const size_t smem = ((size_t)LA_C * (((dim + 3) & ~3) + dim + 1) + (size_t)dim * LA_C + LA_C * LA_EV + LA_C * (LA_C + 1) +
+                         (size_t)dim * LA_EV + LA_C + 1) * sizeof(float);
     dim3 grid(n_seqs, heads, vsplits * p.segments);
     cudaStream_t s = (cudaStream_t)stream;
     const int rc = dtype == LLMK_F32 ? dispatch_linear_attention<float>(p, grid, smem, s) : dispatch_linear_attention<bf16>(p, grid, smem, s);
