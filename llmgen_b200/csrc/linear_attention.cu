@@ -304,10 +304,10 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(Li
 // i counting inside the segment.  One block per (sequence, head, 32 value columns x segment), chunks of 32 tokens.
 template <typename T>
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_carry_kernel(LinAttnParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int D = p.dim, E = p.vdim;
-    const int DP = D + 1;
-    float* Qs = smem;                      // [C][D + 1]
+    const int DP = (D + 3) & ~3;           // rows of q, read as float4 broadcasts
+    float* Qs = smem;                      // [C][DP]
     float* Ss = Qs + LA_C * DP;            // [D][EV]
     const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int vsplits = ceil_div(E, LA_EV);
@@ -361,7 +361,16 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_carry_kernel(L
         float acc[LA_C / LA_WARPS];
 #pragma unroll
         for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = 0.f;
-        for (int d = 0; d < D; ++d) {
+        for (int d4 = 0; d4 < D / 4; ++d4) {
+            const float s0 = Ss[(4 * d4) * LA_EV + lane], s1 = Ss[(4 * d4 + 1) * LA_EV + lane];
+            const float s2 = Ss[(4 * d4 + 2) * LA_EV + lane], s3 = Ss[(4 * d4 + 3) * LA_EV + lane];
+#pragma unroll
+            for (int r = 0; r < LA_C / LA_WARPS; ++r) {
+                const float4 q = *reinterpret_cast<const float4*>(Qs + (g + LA_WARPS * r) * DP + 4 * d4);
+                acc[r] = fmaf(q.x, s0, acc[r]); acc[r] = fmaf(q.y, s1, acc[r]); acc[r] = fmaf(q.z, s2, acc[r]); acc[r] = fmaf(q.w, s3, acc[r]);
+            }
+        }
+        for (int d = D & ~3; d < D; ++d) {
             const float sv = Ss[d * LA_EV + lane];
 #pragma unroll
             for (int r = 0; r < LA_C / LA_WARPS; ++r) acc[r] = fmaf(Qs[(g + LA_WARPS * r) * DP + d], sv, acc[r]);
@@ -433,7 +442,7 @@ LLMK_EXPORT int llmk_linear_attention(float* out, const void* q, const void* k, 
     if (rc != LLMK_OK || p.segments == 1) return rc;
     LLMK_CHECK_LAUNCH_RC("linear_attention_scan", llmk_launch(linear_attention_scan_kernel, dim3(n_seqs, heads, ceil_div(dim * vdim, LA_WARPS * 32)),
                                                               dim3(LA_WARPS * 32), 0, s, true, p));
-    const size_t smem_c = ((size_t)LA_C * (dim + 1) + (size_t)dim * LA_EV) * sizeof(float);
+    const size_t smem_c = ((size_t)LA_C * ((dim + 3) & ~3) + (size_t)dim * LA_EV) * sizeof(float);
     if (dtype == LLMK_F32) {
         if (smem_c > 48 * 1024) cudaFuncSetAttribute(linear_attention_carry_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
         LLMK_CHECK_LAUNCH_RC("linear_attention_carry", llmk_launch(linear_attention_carry_kernel<float>, grid, dim3(LA_WARPS * 32), smem_c, s, true, p));
