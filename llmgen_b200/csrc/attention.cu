@@ -19,6 +19,11 @@
 // sequence's own keys) and writes un-normalised partial sums
 // and (m, l); `llmk_attention_reduce` merges them as
 // sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p (attention.cu:186-207 in the reference).
+//
+// Variations a model may switch on: values of another width than keys (`vd`); a bound on the scores,
+// s <- softcap * tanh(s / softcap) after the scale; a sink, one more term exp(0) in the softmax's denominator (a key of
+// score 0 that has no value: the weights of a row then sum to less than one; it enters once, when a row is finished or
+// its parts are merged); an output gate, out <- out * sigmoid(gate) element by element, applied as the row is written.
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()
@@ -39,18 +44,21 @@ struct AttnParams {
     const int* tile_q0;
     float* part_o;
     float* part_ml;
-    long long q_stride, o_stride;
-    int max_blocks, nq, nkv, hd, page_size, window, num_parts, part_size, bq, gc, chunks;
-    float scale;
+    const void* gate;        // [tokens, nq * vd] of the storage type, rows `gate_stride` apart, or null
+    long long q_stride, o_stride, gate_stride;
+    int max_blocks, nq, nkv, hd, vd, page_size, window, num_parts, part_size, bq, gc, chunks, sink;
+    float scale, softcap;
 };
+
+__device__ __forceinline__ float gate_of(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 template <typename T, int HDL>
 __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams p) {
     extern __shared__ float smem[];
-    const int hd = p.hd;
+    const int hd = p.hd, vd = p.vd;
     float* Qs = smem;                       // [MAX_ROWS][hd], pre-multiplied by scale
     float* Ks = Qs + MAX_ROWS * hd;         // [KT][hd + 1]
-    float* Vs = Ks + KT * (hd + 1);         // [KT][hd]
+    float* Vs = Ks + KT * (hd + 1);         // [KT][vd]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int s = p.tile_seq[blockIdx.x];
     if (s < 0) return;                      // padding of a tile list of fixed length
@@ -111,30 +119,28 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
         for (int j = 0; j < HDL; ++j) acc[i][j] = 0.f;
 
     constexpr int VN = Vec16<T>::N;
-    const int vecs = hd / VN;
+    const int vecs = hd / VN, vvecs = vd / VN;
     for (int t0 = k_beg; t0 < k_end; t0 += KT) {
         __syncthreads();  // previous tile consumed (and Qs written, first time)
-        for (int idx = threadIdx.x; idx < KT * vecs; idx += blockDim.x) {
-            const int key = idx / vecs, vec = idx % vecs;
+        for (int idx = threadIdx.x; idx < KT * (vecs + vvecs); idx += blockDim.x) {
+            const int key = idx / (vecs + vvecs), vec = idx % (vecs + vvecs);
+            const bool is_k = vec < vecs;
             const int kpos = t0 + key;
-            float kf[VN], vf[VN];
+            float f[VN];
             if (kpos < k_end) {
                 const int page = bt[kpos / p.page_size];
-                const size_t off = (((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size) * hd + (size_t)vec * VN;
-                Vec16<T> kv, vv;
-                kv.raw = *reinterpret_cast<const decltype(kv.raw)*>(kc + off);
-                vv.raw = *reinterpret_cast<const decltype(vv.raw)*>(vc + off);
-                kv.unpack(kf);
-                vv.unpack(vf);
+                const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
+                Vec16<T> v;
+                v.raw = is_k ? *reinterpret_cast<const decltype(v.raw)*>(kc + row * hd + (size_t)vec * VN)
+                             : *reinterpret_cast<const decltype(v.raw)*>(vc + row * vd + (size_t)(vec - vecs) * VN);
+                v.unpack(f);
             } else {
 #pragma unroll
-                for (int i = 0; i < VN; ++i) kf[i] = vf[i] = 0.f;
+                for (int i = 0; i < VN; ++i) f[i] = 0.f;
             }
+            float* dst = is_k ? Ks + key * (hd + 1) + vec * VN : Vs + key * vd + (vec - vecs) * VN;
 #pragma unroll
-            for (int i = 0; i < VN; ++i) {
-                Ks[key * (hd + 1) + vec * VN + i] = kf[i];
-                Vs[key * hd + vec * VN + i] = vf[i];
-            }
+            for (int i = 0; i < VN; ++i) dst[i] = f[i];
         }
         __syncthreads();
         if (!valid[0] && !valid[1]) continue;
@@ -152,6 +158,10 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
                 sc[1] = fmaf(b.x, k0, sc[1]); sc[1] = fmaf(b.y, k1, sc[1]);
                 sc[1] = fmaf(b.z, k2, sc[1]); sc[1] = fmaf(b.w, k3, sc[1]);
             }
+        }
+        if (p.softcap > 0.f) {
+            sc[0] = p.softcap * tanhf(sc[0] / p.softcap);
+            sc[1] = p.softcap * tanhf(sc[1] / p.softcap);
         }
         const int kpos = t0 + lane;
         float pr[2];
@@ -177,11 +187,11 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
         for (int k = 0; k < kmax; ++k) {
             const float p0 = __shfl_sync(0xffffffffu, pr[0], k);
             const float p1 = __shfl_sync(0xffffffffu, pr[1], k);
-            const float* vr = Vs + k * hd;
+            const float* vr = Vs + k * vd;
 #pragma unroll
             for (int j = 0; j < HDL; ++j) {
                 const int d = lane + 32 * j;
-                if (d < hd) {
+                if (d < vd) {
                     const float v = vr[d];
                     acc[0][j] = fmaf(p0, v, acc[0][j]);
                     acc[1][j] = fmaf(p1, v, acc[1][j]);
@@ -202,19 +212,26 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 #pragma unroll
             for (int j = 0; j < HDL; ++j) {
                 const int d = lane + 32 * j;
-                if (d < hd) p.part_o[row * hd + d] = acc[i][j];
+                if (d < vd) p.part_o[row * vd + d] = acc[i][j];
             }
             if (lane == 0) {
                 p.part_ml[row * 2] = m[i];
                 p.part_ml[row * 2 + 1] = l[i];
             }
         } else {
-            T* o = static_cast<T*>(p.out) + tok * p.o_stride + (size_t)head_of[i] * hd;
-            const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+            T* o = static_cast<T*>(p.out) + tok * p.o_stride + (size_t)head_of[i] * vd;
+            const T* g = p.gate ? static_cast<const T*>(p.gate) + tok * p.gate_stride + (size_t)head_of[i] * vd : nullptr;
+            float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+            if (p.sink && l[i] > 0.f) {
+                // the sink's score is 0: with M = max(m, 0), weights are e^(s - M) / (l e^(m - M) + e^(-M))
+                const float M = fmaxf(m[i], 0.f);
+                const float w = expf(m[i] - M);
+                inv = w / (l[i] * w + expf(-M));
+            }
 #pragma unroll
             for (int j = 0; j < HDL; ++j) {
                 const int d = lane + 32 * j;
-                if (d < hd) o[d] = from_float<T>(acc[i][j] * inv);
+                if (d < vd) o[d] = from_float<T>(acc[i][j] * inv * (g ? gate_of(to_float(g[d])) : 1.f));
             }
         }
     }
@@ -224,7 +241,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 template <typename T>
 __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride, const float* __restrict__ part_o,
                                         const float* __restrict__ part_ml, int n_rows, int nq, int hd,
-                                        int num_parts) {
+                                        int num_parts, int sink, const T* __restrict__ gate, long long gate_stride) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -232,17 +249,20 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride,
     float M = -INFINITY;
     for (int pt = 0; pt < num_parts; ++pt)
         if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
+    if (sink && M > -INFINITY) M = fmaxf(M, 0.f);
     float denom = 0.f;
     for (int pt = 0; pt < num_parts; ++pt)
         if (ml[2 * pt + 1] > 0.f) denom += expf(ml[2 * pt] - M) * ml[2 * pt + 1];
+    if (sink && denom > 0.f) denom += expf(-M);
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
     const size_t tok = (size_t)(row / nq), head = (size_t)(row % nq);
     T* o = out + tok * o_stride + head * hd;
+    const T* g = gate ? gate + tok * gate_stride + head * hd : nullptr;
     for (int d = lane; d < hd; d += 32) {
         float v = 0.f;
         for (int pt = 0; pt < num_parts; ++pt)
             if (ml[2 * pt + 1] > 0.f) v += expf(ml[2 * pt] - M) * part_o[((size_t)row * num_parts + pt) * hd + d];
-        o[d] = from_float<T>(v * inv);
+        o[d] = from_float<T>(v * inv * (g ? gate_of(to_float(g[d])) : 1.f));
     }
 }
 
@@ -261,7 +281,7 @@ static int launch_attention(const AttnParams& p, dim3 grid, size_t smem, cudaStr
 
 template <typename T>
 static int dispatch_attention(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t s) {
-    switch (hdl_of(p.hd)) {
+    switch (hdl_of(p.vd)) {
         case 1: return launch_attention<T, 1>(p, grid, smem, s);
         case 2: return launch_attention<T, 2>(p, grid, smem, s);
         case 4: return launch_attention<T, 4>(p, grid, smem, s);
@@ -279,7 +299,7 @@ LLMK_EXPORT int llmk_attention_tile_queries(int nq, int nkv) {
 }
 
 // Bytes of scratch for `n_tokens` rows split into `num_parts`: partial outputs then (m, l) pairs.
-LLMK_EXPORT long long llmk_attention_scratch_bytes(int n_tokens, int nq, int hd, int num_parts) {
+LLMK_EXPORT long long llmk_attention_scratch_bytes(int n_tokens, int nq, int hd, int num_parts) {   // hd: the values' width
     if (num_parts <= 1) return 0;
     return (long long)n_tokens * nq * num_parts * (hd + 2) * (long long)sizeof(float);
 }
@@ -289,8 +309,12 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      int max_blocks, const int* ctx_len, const int* cu_q, const int* tile_seq,
                                      const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int hd,
                                      int page_size, int window, float scale, int num_parts, int part_size,
-                                     void* scratch, int dtype, void* stream) {
+                                     void* scratch, int vd, float softcap, int sink, const void* gate, long long gate_stride,
+                                     int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
+    if (vd <= 0) vd = hd;
+    if (vd % 8 != 0 || vd > 512) LLMK_FAIL("paged_attention: value width %d must be a multiple of 8, at most 512", vd);
+    if (softcap < 0.f) LLMK_FAIL("paged_attention: softcap %g", (double)softcap);
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     if (hd <= 0 || hd % 8 != 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be a multiple of 8, at most 512", hd);
     if (page_size <= 0) LLMK_FAIL("paged_attention: page_size %d", page_size);
@@ -304,11 +328,12 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     p.q = q; p.kcache = kcache; p.vcache = vcache; p.out = out;
     p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
     p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
-    p.nq = nq; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.window = window;
+    p.nq = nq; p.nkv = nkv; p.hd = hd; p.vd = vd; p.page_size = page_size; p.window = window;
+    p.softcap = softcap; p.sink = sink ? 1 : 0; p.gate = gate; p.gate_stride = gate_stride;
     p.num_parts = num_parts; p.part_size = part_size; p.scale = scale;
     p.part_o = (float*)scratch;
-    p.part_ml = num_parts > 1 ? (float*)scratch + (size_t)n_tokens * nq * num_parts * hd : nullptr;
-    const size_t smem = ((size_t)MAX_ROWS * hd + (size_t)KT * (hd + 1) + (size_t)KT * hd) * sizeof(float);
+    p.part_ml = num_parts > 1 ? (float*)scratch + (size_t)n_tokens * nq * num_parts * vd : nullptr;
+    const size_t smem = ((size_t)MAX_ROWS * hd + (size_t)KT * (hd + 1) + (size_t)KT * vd) * sizeof(float);
     dim3 grid(n_tiles, nkv * p.chunks, num_parts);
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
@@ -325,9 +350,11 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
         const int warps = 4;
         const int blocks = ceil_div(n_rows, warps);
         if (dtype == LLMK_F32)
-            attention_reduce_kernel<float><<<blocks, warps * 32, 0, s>>>((float*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, hd, num_parts);
+            attention_reduce_kernel<float><<<blocks, warps * 32, 0, s>>>((float*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
+                                                                         p.sink, (const float*)gate, gate_stride);
         else
-            attention_reduce_kernel<bf16><<<blocks, warps * 32, 0, s>>>((bf16*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, hd, num_parts);
+            attention_reduce_kernel<bf16><<<blocks, warps * 32, 0, s>>>((bf16*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
+                                                                        p.sink, (const bf16*)gate, gate_stride);
         LLMK_CHECK_LAUNCH("attention_reduce");
     }
     return LLMK_OK;

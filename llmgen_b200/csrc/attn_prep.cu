@@ -9,7 +9,8 @@
 // heads; here any head_dim up to 512 that is a multiple of 2, any head counts, and a rotary
 // width below the head width (src/module/rope.zig:86-88) are taken.
 //
-// Layouts: qkv[t] = [q heads | k heads | v heads], each head `hd` values, row stride given;
+// Layouts: qkv[t] = [q heads | k heads | v heads], each head `hd` values (value heads `vd`, where that differs), row
+// stride given; an optional float32 bias over the packed columns is added first (the projections' biases);
 // q is normalised and rotated into `q_out` (which may be the packed rows themselves).  The packed
 // rows are of the storage type T, or (splits > 0) `splits` float32 slices [splits][n][row_stride],
 // `split_stride` floats apart, added in slice order: the partial sums of a projection cut along K.
@@ -44,7 +45,8 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
                                  const int* __restrict__ slots, const float* __restrict__ cos_tab,
                                  const float* __restrict__ sin_tab, const float* __restrict__ q_gain,
                                  const float* __restrict__ k_gain, int n_tokens, int nq, int nk, int nkv_cache,
-                                 int hd, int rot, int page_size, float eps, float q_off, float k_off) {
+                                 int hd, int rot, int page_size, float eps, float q_off, float k_off,
+                                 const float* __restrict__ bias, int vd) {
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int heads = nq + 2 * nk;
@@ -54,19 +56,23 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
     const int h = (int)(item % heads);
     pdl_launch_dependents();
     pdl_wait();
+    // where the head's values begin in a packed row (and in the bias): value heads are `vd` wide and come last
+    const size_t col0 = h < nq + nk ? (size_t)h * hd : (size_t)(nq + nk) * hd + (size_t)(h - nq - nk) * vd;
     PackedRow<T> x;
-    x.x = static_cast<const T*>(qkv) + (size_t)t * row_stride + (size_t)h * hd;
-    x.p = static_cast<const float*>(qkv) + (size_t)t * row_stride + (size_t)h * hd;
+    x.x = static_cast<const T*>(qkv) + (size_t)t * row_stride + col0;
+    x.p = static_cast<const float*>(qkv) + (size_t)t * row_stride + col0;
     x.splits = splits;
     x.split_stride = split_stride;
+    const float* hb = bias ? bias + col0 : nullptr;
     const int slot = slots ? slots[t] : -1;
 
     if (h >= nq + nk) {  // a value head: copy into the cache
         if (slot < 0 || !vcache) return;
         const int kvh = h - nq - nk;
-        T* dst = vcache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
+        T* dst = vcache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * vd;
         if (splits == 0) {
-            for (int i = lane; i < hd; i += 32) dst[i] = x.x[i];
+            if (hb) for (int i = lane; i < vd; i += 32) dst[i] = from_float<T>(to_float(x.x[i]) + hb[i]);
+            else for (int i = lane; i < vd; i += 32) dst[i] = x.x[i];
             return;
         }
         float vv[MAX_TAIL];
@@ -77,11 +83,11 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
             const float* ps = x.p + (size_t)sp * split_stride;
 #pragma unroll
             for (int i = 0; i < MAX_TAIL; ++i)
-                if (lane + 32 * i < hd) vv[i] += __ldcg(ps + lane + 32 * i);
+                if (lane + 32 * i < vd) vv[i] += __ldcg(ps + lane + 32 * i);
         }
 #pragma unroll
         for (int i = 0; i < MAX_TAIL; ++i)
-            if (lane + 32 * i < hd) dst[lane + 32 * i] = from_float<T>(vv[i]);
+            if (lane + 32 * i < vd) dst[lane + 32 * i] = from_float<T>(vv[i] + (hb ? hb[lane + 32 * i] : 0.f));
         return;
     }
     const bool is_q = h < nq;
@@ -127,6 +133,21 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
                 const int e = rot + lane + 32 * i;
                 if (e < hd) tail[i] += __ldcg(ps + e);
             }
+        }
+    }
+    if (hb) {
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i) {
+            const int p = lane + 32 * i;
+            if (p < half) {
+                a[i] += hb[p];
+                b[i] += hb[p + half];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) {
+            const int e = rot + lane + 32 * i;
+            if (e < hd) tail[i] += hb[e];
         }
     }
 #pragma unroll
@@ -455,9 +476,11 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
                                long long q_stride, void* kcache, void* vcache, const int* positions,
                                const int* slots, const float* cos_tab, const float* sin_tab, const float* q_gain,
                                const float* k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd, int rot,
-                               int page_size, float eps, float q_off, float k_off, int pairing, int head_norm, int dtype,
-                               void* stream) {
+                               int page_size, float eps, float q_off, float k_off, int pairing, int head_norm,
+                               const float* bias, int vd, int dtype, void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
+    if (vd <= 0) vd = hd;
+    if (vd > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: value width %d too large", vd);
     if (pairing != LLMK_PAIR_HALF_SPLIT)
         LLMK_FAIL("attn_prep: rotary pairing %d is not built (0: half-split, pairs (i, i + rot / 2))", pairing);
     if (head_norm != LLMK_HEAD_NORM_RMS) LLMK_FAIL("attn_prep: per-head norm kind %d is not built (0: RMSNorm)", head_norm);
@@ -476,7 +499,7 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 2147483647LL) LLMK_FAIL("attn_prep: too many rows");
     cudaError_t e;
-    if (splits == 0 && n_tokens >= 32) {
+    if (splits == 0 && n_tokens >= 32 && !bias && vd == hd) {
         bool taken = false;
         if (dtype == LLMK_F32)
             taken = launch_vec<float>(qkv, row_stride, q_out, q_stride, kcache, vcache, positions, slots, cos_tab, sin_tab,
@@ -493,12 +516,12 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
         e = llmk_launch(attn_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
                         splits, split_stride, (float*)q_out, q_stride, (float*)kcache, (float*)vcache, positions, slots,
                         cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
-                        k_off);
+                        k_off, bias, vd);
     else if (dtype == LLMK_BF16)
         e = llmk_launch(attn_prep_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
                         splits, split_stride, (bf16*)q_out, q_stride, (bf16*)kcache, (bf16*)vcache, positions, slots,
                         cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
-                        k_off);
+                        k_off, bias, vd);
     else
         LLMK_FAIL("attn_prep: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("attn_prep", e);

@@ -51,22 +51,24 @@ LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, c
     return LLMK_OK;
 }
 
-// x = cap * tanh(x / cap) on float32 logits, in place: an architecture's bound on its logits (none here has one;
-// `ModelSpec.logit_cap` is the slot).
-__global__ void logit_cap_kernel(float* __restrict__ x, long long n, float cap) {
+// x = scale * x, then (cap > 0) x = cap * tanh(x / cap), on float32 logits in place: an architecture's factor on its
+// logits and its bound on them (`ModelSpec.logit_scale`, `ModelSpec.logit_cap`).
+__global__ void logit_cap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
     pdl_launch_dependents();
     pdl_wait();
-    const float inv = 1.0f / cap;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        x[i] = cap * tanhf(x[i] * inv);
+    const float inv = cap > 0.f ? 1.0f / cap : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = x[i] * scale;
+        x[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
+    }
 }
 
-LLMK_EXPORT int llmk_logit_cap(float* x, long long n, float cap, void* stream) {
+LLMK_EXPORT int llmk_logit_cap(float* x, long long n, float scale, float cap, void* stream) {
     if (n <= 0) return LLMK_OK;
-    if (!(cap > 0.f)) LLMK_FAIL("logit_cap: the cap must be positive, got %g", (double)cap);
+    if (cap < 0.f) LLMK_FAIL("logit_cap: the cap must be positive (0: none), got %g", (double)cap);
     long long blocks = (n + 255) / 256;
     if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
-    LLMK_CHECK_LAUNCH_RC("logit_cap", llmk_launch(logit_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, true, x, n, cap));
+    LLMK_CHECK_LAUNCH_RC("logit_cap", llmk_launch(logit_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, true, x, n, scale, cap));
     return LLMK_OK;
 }
 

@@ -1,0 +1,461 @@
+// Kernels of mixers that carry a fixed-size state from token to token instead of reading a cache of keys:
+//
+//   short_conv          a causal convolution over time on each channel by itself, whose first tokens of a step read the
+//                       last inputs of the step before out of the request's state
+//   conv_state_update   leaves the last K - 1 inputs of every sequence in its state
+//   rglru_gates         per block of channels two small square products (recurrence gate and input gate) and from them
+//                       the coefficients of the recurrence  S_t = a_t S_(t-1) + b_t
+//   rglru_scan          that recurrence over each sequence's new tokens, times the other branch's gelu
+//   delta_scan          the gated delta rule with a decay per key channel:
+//                       S <- diag(g) S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q
+//
+// A step's sequences are given as everywhere else: sequence s owns token rows [cu_q[s], cu_q[s+1]), its state lies in
+// slot state_slots[s] (-1: none; the sequence then starts from zeros and leaves nothing).  Rows beyond cu_q[n_seqs]
+// belong to no sequence and are skipped, sequences without tokens too, so every launch here follows from a step's shape.
+// Every state is float32; gates, decays, their logarithms and exponentials, unit norms and the recurrences are float32
+// arithmetic in both storage dtypes.  The arithmetic of a token does not depend on where a step was cut.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+constexpr int MAX_TAPS = 8;
+
+__device__ __forceinline__ int seq_of_row(const int* __restrict__ cu_q, int n_seqs, int t) {
+    if (t >= cu_q[n_seqs]) return -1;
+    int lo = 0, hi = n_seqs;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cu_q[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float gelu_tanhf_(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution
+// out[t, c] = act( sum_i taps[c, i] in(j - (K-1) + i, c) + conv_bias[c] ), j the token's index in its portion;
+// in(r, c) = x[row of r, c] + in_bias[c] for r >= 0, else the state's row K - 1 + r (zeros for a fresh request).
+template <typename T>
+__global__ void short_conv_kernel(float* __restrict__ out, long long out_ld, const T* __restrict__ x, long long x_ld,
+                                  const float* __restrict__ in_bias, const float* __restrict__ taps,
+                                  const float* __restrict__ conv_bias, const float* __restrict__ state, long long state_ld,
+                                  const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs, int C, int K,
+                                  int act) {
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int s = seq_of_row(cu_q, n_seqs, t);
+    if (s < 0) return;
+    const int q_beg = cu_q[s];
+    const int j = t - q_beg;
+    const int slot = state_slots[s];
+    const float b = in_bias ? in_bias[c] : 0.f;
+    float acc = conv_bias ? conv_bias[c] : 0.f;
+    for (int i = 0; i < K; ++i) {
+        const int r = j - (K - 1) + i;
+        float v;
+        if (r >= 0) v = to_float(x[(size_t)(q_beg + r) * x_ld + c]) + b;
+        else v = slot >= 0 ? state[(size_t)slot * state_ld + (size_t)(K - 1 + r) * C + c] : 0.f;
+        acc = fmaf(taps[(size_t)c * K + i], v, acc);
+    }
+    out[(size_t)t * out_ld + c] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(float* __restrict__ state, long long state_ld, const T* __restrict__ x, long long x_ld,
+                                         const float* __restrict__ in_bias, const int* __restrict__ cu_q,
+                                         const int* __restrict__ state_slots, int C, int K) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    const int slot = state_slots[s];
+    if (n <= 0 || slot < 0) return;
+    float* st = state + (size_t)slot * state_ld + c;
+    const float b = in_bias ? in_bias[c] : 0.f;
+    float old[MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS - 1; ++i) old[i] = i < K - 1 ? st[(size_t)i * C] : 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS - 1; ++i) {
+        if (i >= K - 1) break;
+        const int idx = n + i - (K - 1);      // among the step's own inputs
+        float v;
+        if (idx >= 0) v = to_float(x[(size_t)(q_beg + idx) * x_ld + c]) + b;
+        else v = old[n + i];
+        st[(size_t)i * C] = v;
+    }
+}
+
+LLMK_EXPORT int llmk_short_conv(float* out, long long out_ld, const void* x, long long x_ld, const float* in_bias,
+                                const float* taps, const float* conv_bias, float* state, long long state_ld, const int* cu_q,
+                                const int* state_slots, int n_seqs, int n_tokens, int C, int K, int act, int update_state,
+                                int dtype, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0 || C <= 0) return LLMK_OK;
+    if (K < 1 || K > MAX_TAPS) LLMK_FAIL("short_conv: %d taps (1 to %d are built)", K, MAX_TAPS);
+    if (!out || !x || !taps || !state || !cu_q || !state_slots) LLMK_FAIL("short_conv: bad arguments");
+    if (act != 0 && act != 1) LLMK_FAIL("short_conv: unknown activation %d (0: none, 1: silu)", act);
+    if (n_tokens > 65535 || n_seqs > 65535) LLMK_FAIL("short_conv: a step of %d tokens in %d sequences is too large", n_tokens, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 128;
+    dim3 grid(ceil_div(C, threads), n_tokens), ugrid(ceil_div(C, threads), n_seqs);
+    cudaError_t e;
+    if (dtype == LLMK_F32) {
+        e = llmk_launch(short_conv_kernel<float>, grid, dim3(threads), 0, s, true, out, out_ld, (const float*)x, x_ld, in_bias, taps,
+                        conv_bias, (const float*)state, state_ld, cu_q, state_slots, n_seqs, C, K, act);
+        if (e == cudaSuccess && update_state && K > 1)
+            e = llmk_launch(conv_state_update_kernel<float>, ugrid, dim3(threads), 0, s, true, state, state_ld, (const float*)x, x_ld,
+                            in_bias, cu_q, state_slots, C, K);
+    } else if (dtype == LLMK_BF16) {
+        e = llmk_launch(short_conv_kernel<bf16>, grid, dim3(threads), 0, s, true, out, out_ld, (const bf16*)x, x_ld, in_bias, taps,
+                        conv_bias, (const float*)state, state_ld, cu_q, state_slots, n_seqs, C, K, act);
+        if (e == cudaSuccess && update_state && K > 1)
+            e = llmk_launch(conv_state_update_kernel<bf16>, ugrid, dim3(threads), 0, s, true, state, state_ld, (const bf16*)x, x_ld,
+                            in_bias, cu_q, state_slots, C, K);
+    } else
+        LLMK_FAIL("short_conv: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("short_conv", e);
+    return LLMK_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ RG-LRU
+// Block (tile of `GATE_OUT` outputs, block of channels b, tile of TT tokens): r = sigmoid(Ra_b u_b + ba), i = sigmoid(Ri_b u_b + bi),
+// log a = -scale r softplus(lam), a = exp(log a), b = sqrt(1 - a^2) i u  (1 - a^2 as -expm1(2 log a): no cancellation near a = 1).
+constexpr int GATE_OUT = 128;
+
+template <typename T, int TT>
+__global__ void __launch_bounds__(GATE_OUT) rglru_gates_kernel(float* __restrict__ a_out, float* __restrict__ b_out,
+                                                               const float* __restrict__ u, const T* __restrict__ Wa,
+                                                               const T* __restrict__ Wi, const float* __restrict__ ba,
+                                                               const float* __restrict__ bi, const float* __restrict__ lam,
+                                                               int n_tokens, int C, int n, float decay_scale, int vec_ok) {
+    extern __shared__ float Us[];   // [TT][n]
+    const int b = blockIdx.y, t0 = blockIdx.z * TT;
+    const int o = blockIdx.x * GATE_OUT + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < TT * n; idx += GATE_OUT) {
+        const int tt = idx / n, k = idx % n;
+        Us[idx] = t0 + tt < n_tokens ? u[(size_t)(t0 + tt) * C + (size_t)b * n + k] : 0.f;
+    }
+    __syncthreads();
+    if (o >= n) return;
+    float accA[TT], accI[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) accA[tt] = accI[tt] = 0.f;
+    const T* wa = Wa + ((size_t)b * n + o) * n;
+    const T* wi = Wi + ((size_t)b * n + o) * n;
+    constexpr int VN = Vec16<T>::N;
+    int k = 0;
+    if (vec_ok) {
+        for (; k + VN <= n; k += VN) {
+            Vec16<T> va, vi;
+            va.raw = *reinterpret_cast<const decltype(va.raw)*>(wa + k);
+            vi.raw = *reinterpret_cast<const decltype(vi.raw)*>(wi + k);
+            float fa[VN], fi[VN];
+            va.unpack(fa);
+            vi.unpack(fi);
+#pragma unroll
+            for (int j = 0; j < VN; ++j)
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) {
+                    const float uv = Us[tt * n + k + j];
+                    accA[tt] = fmaf(fa[j], uv, accA[tt]);
+                    accI[tt] = fmaf(fi[j], uv, accI[tt]);
+                }
+        }
+    }
+    for (; k < n; ++k) {
+        const float fa = to_float(wa[k]), fi = to_float(wi[k]);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            const float uv = Us[tt * n + k];
+            accA[tt] = fmaf(fa, uv, accA[tt]);
+            accI[tt] = fmaf(fi, uv, accI[tt]);
+        }
+    }
+    const int c = b * n + o;
+    const float sp = softplusf_(lam[c]);
+    const float bias_a = ba ? ba[c] : 0.f, bias_i = bi ? bi[c] : 0.f;
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        const int t = t0 + tt;
+        if (t >= n_tokens) break;
+        const float r = sigmoidf_(accA[tt] + bias_a);
+        const float ig = sigmoidf_(accI[tt] + bias_i);
+        const float loga = -decay_scale * r * sp;
+        a_out[(size_t)t * C + c] = expf(loga);
+        b_out[(size_t)t * C + c] = sqrtf(-expm1f(2.0f * loga)) * ig * Us[tt * n + o];
+    }
+}
+
+// Thread (sequence, channel): S = a S + b over the sequence's new tokens, out = S * gelu_tanh(y + y_bias).
+template <typename T>
+__global__ void rglru_scan_kernel(T* __restrict__ out, long long out_ld, const float* __restrict__ a, const float* __restrict__ bx,
+                                  const T* __restrict__ y, long long y_ld, const float* __restrict__ y_bias,
+                                  float* __restrict__ state, long long state_ld, const int* __restrict__ cu_q,
+                                  const int* __restrict__ state_slots, int C) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int q_beg = cu_q[s], q_end = cu_q[s + 1];
+    if (q_end <= q_beg) return;
+    const int slot = state_slots[s];
+    float S = slot >= 0 ? state[(size_t)slot * state_ld + c] : 0.f;
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    int t = q_beg;
+    for (; t + 4 <= q_end; t += 4) {
+        float av[4], bv[4], yv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            av[i] = a[(size_t)(t + i) * C + c];
+            bv[i] = bx[(size_t)(t + i) * C + c];
+            yv[i] = to_float(y[(size_t)(t + i) * y_ld + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            S = fmaf(av[i], S, bv[i]);
+            out[(size_t)(t + i) * out_ld + c] = from_float<T>(S * gelu_tanhf_(yv[i] + yb));
+        }
+    }
+    for (; t < q_end; ++t) {
+        S = fmaf(a[(size_t)t * C + c], S, bx[(size_t)t * C + c]);
+        out[(size_t)t * out_ld + c] = from_float<T>(S * gelu_tanhf_(to_float(y[(size_t)t * y_ld + c]) + yb));
+    }
+    if (slot >= 0) state[(size_t)slot * state_ld + c] = S;
+}
+
+template <typename T>
+static int launch_rglru(void* out, long long out_ld, float* a_buf, float* b_buf, const float* u, const void* Wa, const void* Wi,
+                        const float* ba, const float* bi, const float* lam, const void* y, long long y_ld, const float* y_bias,
+                        float* state, long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int C,
+                        int blocks, float decay_scale, cudaStream_t s) {
+    const int n = C / blocks;
+    constexpr int VN = Vec16<T>::N;
+    const int vec_ok = (n % VN == 0 && host_aligned16(Wa) && host_aligned16(Wi)) ? 1 : 0;
+    // tokens a block of the gates' kernel takes: as many as keep its rows of u within 64 KB of shared memory
+    int tt = 16;
+    while (tt > 1 && (size_t)tt * n * sizeof(float) > 64 * 1024) tt >>= 1;
+    if (n_tokens <= 4 && tt > 4) tt = 4;
+    const size_t smem = (size_t)tt * n * sizeof(float);
+    if (smem > 200 * 1024) LLMK_FAIL("rglru: blocks of %d channels do not fit shared memory", n);
+    dim3 ggrid(ceil_div(n, GATE_OUT), blocks, ceil_div(n_tokens, tt));
+    if (ggrid.z > 65535) LLMK_FAIL("rglru: a step of %d tokens is too large", n_tokens);
+    cudaError_t e;
+#define LAUNCH_GATES(TTV)                                                                                                       \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(rglru_gates_kernel<T, TTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        e = llmk_launch(rglru_gates_kernel<T, TTV>, ggrid, dim3(GATE_OUT), smem, s, true, a_buf, b_buf, u, (const T*)Wa, (const T*)Wi, \
+                        ba, bi, lam, n_tokens, C, n, decay_scale, vec_ok);                                                        \
+    } while (0)
+    if (tt == 16) LAUNCH_GATES(16);
+    else if (tt == 8) LAUNCH_GATES(8);
+    else if (tt == 4) LAUNCH_GATES(4);
+    else if (tt == 2) LAUNCH_GATES(2);
+    else LAUNCH_GATES(1);
+#undef LAUNCH_GATES
+    LLMK_CHECK_LAUNCH_RC("rglru_gates", e);
+    const int threads = 128;
+    e = llmk_launch(rglru_scan_kernel<T>, dim3(ceil_div(C, threads), n_seqs), dim3(threads), 0, s, true, (T*)out, out_ld,
+                    (const float*)a_buf, (const float*)b_buf, (const T*)y, y_ld, y_bias, state, state_ld, cu_q, state_slots, C);
+    LLMK_CHECK_LAUNCH_RC("rglru_scan", e);
+    return LLMK_OK;
+}
+
+// out[t, c] (storage dtype) = S_t[c] * gelu_tanh(y[t, c] + y_bias[c]);  u float32 [n_tokens, C] is the convolution's output;
+// a_buf, b_buf: float32 scratch [n_tokens, C] each.
+LLMK_EXPORT int llmk_rglru(void* out, long long out_ld, float* a_buf, float* b_buf, const float* u, const void* Wa, const void* Wi,
+                           const float* ba, const float* bi, const float* lam, const void* y, long long y_ld, const float* y_bias,
+                           float* state, long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int C,
+                           int blocks, float decay_scale, int dtype, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return LLMK_OK;
+    if (C <= 0 || blocks <= 0 || C % blocks != 0) LLMK_FAIL("rglru: %d channels are not cut evenly into %d blocks", C, blocks);
+    if (!out || !a_buf || !b_buf || !u || !Wa || !Wi || !lam || !y || !state || !cu_q || !state_slots) LLMK_FAIL("rglru: bad arguments");
+    if (n_seqs > 65535 || blocks > 65535) LLMK_FAIL("rglru: grid too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == LLMK_F32)
+        return launch_rglru<float>(out, out_ld, a_buf, b_buf, u, Wa, Wi, ba, bi, lam, y, y_ld, y_bias, state, state_ld, cu_q,
+                                   state_slots, n_seqs, n_tokens, C, blocks, decay_scale, s);
+    if (dtype == LLMK_BF16)
+        return launch_rglru<bf16>(out, out_ld, a_buf, b_buf, u, Wa, Wi, ba, bi, lam, y, y_ld, y_bias, state, state_ld, cu_q,
+                                  state_slots, n_seqs, n_tokens, C, blocks, decay_scale, s);
+    LLMK_FAIL("rglru: unknown dtype %d", dtype);
+}
+
+// ------------------------------------------------------------------------------------------------ gated delta rule
+// Block (sequence, head, tile of 64 value columns), 256 threads: a lane holds a quarter of one column of S (key channels
+// slice, slice + 4, ...), so the two dot products of a token over the key channels end in two shuffles.  The tokens of
+// a portion come in chunks of DELTA_CHUNK: all threads first prepare the chunk in shared memory (q and k made unit
+// vectors, q scaled, the decays exponentiated, beta through its sigmoid), then the columns walk the chunk token by token.
+constexpr int DELTA_CHUNK = 16;
+constexpr int DELTA_COLS = 64;
+
+struct DeltaParams {
+    float* out;              // [n_tokens, H * E]
+    const float* qkv;        // [n_tokens, ld]: q at column 0, k at G * D, v at 2 * G * D (after convolution and silu)
+    long long qkv_ld;
+    const void* beta;        // [n_tokens, ldb] storage dtype, column h
+    long long beta_ld;
+    const float* decay;      // [n_tokens, H * D] float32, before dt_bias and softplus
+    const float* dt_bias;    // [H * D]
+    const float* a_log;      // [H]
+    float* state;            // [slots, state_ld]: S [H][D][E]
+    long long state_ld;
+    const int* cu_q;
+    const int* state_slots;
+    int H, G, D, E;
+    float unit_eps, q_scale;
+};
+
+template <typename T, int DSL>
+__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
+    constexpr int DP = 4 * DSL;
+    extern __shared__ float sm[];
+    float* qs = sm;                                  // [CHUNK][DP]
+    float* ks = qs + DELTA_CHUNK * DP;
+    float* gs = ks + DELTA_CHUNK * DP;
+    float* vs = gs + DELTA_CHUNK * DP;               // [CHUNK][COLS]
+    float* betas = vs + DELTA_CHUNK * DELTA_COLS;    // [CHUNK]
+    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * DELTA_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slice = lane & 3, col = warp * 8 + (lane >> 2);
+    const int e = e0 + col;
+    const int D = p.D, E = p.E;
+    const int kvh = h / (p.H / p.G);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = p.state_slots[s];
+    float S[DSL];
+    float* st = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
+#pragma unroll
+    for (int i = 0; i < DSL; ++i) {
+        const int d = slice + 4 * i;
+        S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
+    }
+    const float neg_exp_a = -expf(p.a_log[h]);
+    const int GD = p.G * D;
+    const T* beta = static_cast<const T*>(p.beta);
+    for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK) {
+        const int nc = min(DELTA_CHUNK, n - c0);
+        __syncthreads();      // the chunk before is consumed
+        for (int idx = threadIdx.x; idx < DELTA_CHUNK * DP; idx += 256) {
+            const int tt = idx / DP, d = idx % DP;
+            float qv = 0.f, kv = 0.f, gv = 1.f;
+            if (tt < nc && d < D) {
+                const size_t t = (size_t)(q_beg + c0 + tt);
+                qv = p.qkv[t * p.qkv_ld + (size_t)kvh * D + d];
+                kv = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
+                gv = expf(neg_exp_a * softplusf_(p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d] + p.dt_bias[(size_t)h * D + d]));
+            }
+            qs[idx] = qv;
+            ks[idx] = kv;
+            gs[idx] = gv;
+        }
+        for (int idx = threadIdx.x; idx < DELTA_CHUNK * DELTA_COLS; idx += 256) {
+            const int tt = idx / DELTA_COLS, cc = idx % DELTA_COLS;
+            vs[idx] = (tt < nc && e0 + cc < E) ? p.qkv[(size_t)(q_beg + c0 + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc] : 0.f;
+        }
+        if (threadIdx.x < DELTA_CHUNK)
+            betas[threadIdx.x] = threadIdx.x < nc ? sigmoidf_(to_float(beta[(size_t)(q_beg + c0 + threadIdx.x) * p.beta_ld + h])) : 0.f;
+        __syncthreads();
+        for (int tt = warp; tt < nc; tt += 8) {      // unit vectors: a warp per token
+            float sq = 0.f, sk = 0.f;
+            for (int d = lane; d < DP; d += 32) {
+                sq += qs[tt * DP + d] * qs[tt * DP + d];
+                sk += ks[tt * DP + d] * ks[tt * DP + d];
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float fq = p.q_scale / sqrtf(sq + p.unit_eps), fk = 1.0f / sqrtf(sk + p.unit_eps);
+            for (int d = lane; d < DP; d += 32) {
+                qs[tt * DP + d] *= fq;
+                ks[tt * DP + d] *= fk;
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; ++tt) {
+            const float* kr = ks + tt * DP + slice;
+            const float* qr = qs + tt * DP + slice;
+            const float* gr = gs + tt * DP + slice;
+            float kS = 0.f;
+#pragma unroll
+            for (int i = 0; i < DSL; ++i) {
+                S[i] *= gr[4 * i];
+                kS = fmaf(kr[4 * i], S[i], kS);
+            }
+            kS += __shfl_xor_sync(0xffffffffu, kS, 1);
+            kS += __shfl_xor_sync(0xffffffffu, kS, 2);
+            const float dlt = betas[tt] * (vs[tt * DELTA_COLS + col] - kS);
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DSL; ++i) {
+                S[i] = fmaf(kr[4 * i], dlt, S[i]);
+                o = fmaf(qr[4 * i], S[i], o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (slice == 0 && e < E) p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = o;
+        }
+    }
+    if (st) {
+#pragma unroll
+        for (int i = 0; i < DSL; ++i) {
+            const int d = slice + 4 * i;
+            if (d < D && e < E) st[(size_t)d * E + e] = S[i];
+        }
+    }
+}
+
+template <typename T, int DSL>
+static cudaError_t launch_delta(const DeltaParams& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = ((size_t)DELTA_CHUNK * (3 * 4 * DSL + DELTA_COLS) + DELTA_CHUNK) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, DSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return llmk_launch(delta_scan_kernel<T, DSL>, grid, dim3(256), smem, s, true, p);
+}
+
+template <typename T>
+static cudaError_t dispatch_delta(const DeltaParams& p, dim3 grid, cudaStream_t s) {
+    if (p.D <= 32) return launch_delta<T, 8>(p, grid, s);
+    if (p.D <= 64) return launch_delta<T, 16>(p, grid, s);
+    if (p.D <= 128) return launch_delta<T, 32>(p, grid, s);
+    return launch_delta<T, 64>(p, grid, s);
+}
+
+// dtype: of `beta` (the storage dtype of the projection it is a column of); everything else is float32.
+LLMK_EXPORT int llmk_delta_scan(float* out, const float* qkv, long long qkv_ld, const void* beta, long long beta_ld, const float* decay,
+                                const float* dt_bias, const float* a_log, float* state, long long state_ld, const int* cu_q,
+                                const int* state_slots, int n_seqs, int H, int G, int D, int E, float unit_eps, float q_scale,
+                                int dtype, void* stream) {
+    if (n_seqs <= 0) return LLMK_OK;
+    if (H <= 0 || G <= 0 || H % G != 0) LLMK_FAIL("delta_scan: %d heads are not a multiple of %d key heads", H, G);
+    if (D <= 0 || D > 256 || E <= 0) LLMK_FAIL("delta_scan: key width %d (at most 256) or value width %d", D, E);
+    if (!out || !qkv || !beta || !decay || !dt_bias || !a_log || !state || !cu_q || !state_slots) LLMK_FAIL("delta_scan: bad arguments");
+    if (H > 65535 || ceil_div(E, DELTA_COLS) > 65535) LLMK_FAIL("delta_scan: grid too large");
+    DeltaParams p;
+    p.out = out; p.qkv = qkv; p.qkv_ld = qkv_ld; p.beta = beta; p.beta_ld = beta_ld; p.decay = decay; p.dt_bias = dt_bias;
+    p.a_log = a_log; p.state = state; p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots;
+    p.H = H; p.G = G; p.D = D; p.E = E; p.unit_eps = unit_eps; p.q_scale = q_scale;
+    dim3 grid(n_seqs, H, ceil_div(E, DELTA_COLS));
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32) e = dispatch_delta<float>(p, grid, s);
+    else if (dtype == LLMK_BF16) e = dispatch_delta<bf16>(p, grid, s);
+    else LLMK_FAIL("delta_scan: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("delta_scan", e);
+    return LLMK_OK;
+}

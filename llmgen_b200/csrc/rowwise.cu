@@ -6,6 +6,9 @@
 //   cast_rows       out = (T) in, float32 in
 //   act_rows        relu(x)^2, or the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L)
 //   gated_rmsnorm   out[r, :] = rmsnorm(o[r, :]) * w * sigmoid(g[r, :])   (or, without gains, o * sigmoid(g))
+//   add_bias        y[r, :] += b, y an array of T or of float32, or the float32 slices of a product (the first slice takes it)
+//   concat_stream   out[r, :] = [ (T)(resid[r, :] + delta[r, :]) | (T) x0[r, :] ]: the operand of a product that mixes the
+//                   residual stream with the embedding's output
 //
 // Sums of squares, gains, the residual and the activations' arithmetic are float32 in both storage dtypes.
 #include "common.cuh"
@@ -93,7 +96,12 @@ LLMK_EXPORT int llmk_cast_rows(void* out, const float* in, long long n, int dtyp
 // mode 0: out[r, f] = relu(x[r, f])^2, x [n, F]
 // mode 1: x [n, 2F], gate in columns [0, F), up in [F, 2F):
 //         g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)
-enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1 };
+// mode 2: x [n, 2F] as in mode 1: out = gelu_tanh(gate) * up, gelu_tanh(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1, ACT_GELU_TANH_GLU = 2 };
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 template <typename T>
 __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x, int n, int F, long long ld, int mode,
@@ -108,6 +116,8 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
         if (mode == ACT_RELU2) {
             const float a = fmaxf(load_sum<T>(x, r * ld + f, splits, split_stride), 0.f);
             v = a * a;
+        } else if (mode == ACT_GELU_TANH_GLU) {
+            v = gelu_tanh(load_sum<T>(x, r * ld + f, splits, split_stride)) * load_sum<T>(x, r * ld + F + f, splits, split_stride);
         } else {
             const float g = fminf(load_sum<T>(x, r * ld + f, splits, split_stride), limit);
             const float u = fminf(fmaxf(load_sum<T>(x, r * ld + F + f, splits, split_stride), -limit), limit);
@@ -120,7 +130,7 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
 LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long ld, int mode, float alpha, float limit,
                               int splits, long long split_stride, int dtype, void* stream) {
     if (n <= 0 || F <= 0) return LLMK_OK;
-    if (mode != ACT_RELU2 && mode != ACT_CLAMPED_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
+    if (mode != ACT_RELU2 && mode != ACT_CLAMPED_GLU && mode != ACT_GELU_TANH_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
     long long blocks = ((long long)n * F + 255) / 256;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
@@ -173,5 +183,67 @@ LLMK_EXPORT int llmk_gated_rmsnorm(void* out, const float* o, const void* g, con
     else
         LLMK_FAIL("gated_rmsnorm: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("gated_rmsnorm", e);
+    return LLMK_OK;
+}
+
+// y[r, i] += b[i].  y is [n, H] of T (rows `ld` apart), or float32 (dtype of the ARRAY, which may differ from the engine's).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ b, int n, int H, long long ld) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)n * H;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const size_t at = (size_t)(i / H) * ld + (size_t)(i % H);
+        y[at] = from_float<T>(to_float(y[at]) + b[i % H]);
+    }
+}
+
+LLMK_EXPORT int llmk_add_bias(void* y, const float* b, int n, int H, long long ld, int dtype, void* stream) {
+    if (n <= 0 || H <= 0) return LLMK_OK;
+    if (!y || !b || ld < H) LLMK_FAIL("add_bias: bad arguments (H %d, ld %lld)", H, ld);
+    long long blocks = ((long long)n * H + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(add_bias_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)y, b, n, H, ld);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(add_bias_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)y, b, n, H, ld);
+    else
+        LLMK_FAIL("add_bias: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("add_bias", e);
+    return LLMK_OK;
+}
+
+template <typename T>
+__global__ void concat_stream_kernel(T* __restrict__ out, const float* __restrict__ resid, const void* __restrict__ delta,
+                                     const float* __restrict__ x0, int n, int H, int splits, long long split_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)n * H;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const size_t r = (size_t)(i / H), c = (size_t)(i % H);
+        float v = resid[i];
+        if (delta) v += load_sum<T>(delta, (size_t)i, splits, split_stride);
+        out[r * 2 * H + c] = from_float<T>(v);
+        out[r * 2 * H + H + c] = from_float<T>(x0[i]);
+    }
+}
+
+LLMK_EXPORT int llmk_concat_stream(void* out, const float* resid, const void* delta, const float* x0, int n, int H, int splits,
+                                   long long split_stride, int dtype, void* stream) {
+    if (n <= 0 || H <= 0) return LLMK_OK;
+    if (!out || !resid || !x0) LLMK_FAIL("concat_stream: bad arguments");
+    long long blocks = ((long long)n * H + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(concat_stream_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, resid, delta, x0, n, H, splits, split_stride);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(concat_stream_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, resid, delta, x0, n, H, splits, split_stride);
+    else
+        LLMK_FAIL("concat_stream: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("concat_stream", e);
     return LLMK_OK;
 }

@@ -18,6 +18,7 @@ from ..kernels import build as kernel_build
 from ..kernels import ops
 from ..parts.base import LayerCache
 from ..parts.linear import linear
+from ..parts.reentry import Reentry
 from ..parts.registry import build_block, build_norm, model_kernel_modules
 from ..parts.spec import ModelSpec
 from .context import StepContext
@@ -34,6 +35,13 @@ class DecoderModel:
         self.device = device
         self.embedding = weights.device_tensor(spec.embedding, dtype, device)
         self.layers = [build_block(ls, weights, dtype, device) for ls in spec.layers]
+        # what a run item does to the residual stream before its layer runs (items with equal specs share one object)
+        made = {}
+        self.before = []
+        for item in spec.run_order:
+            if item.before is not None and item.before not in made:
+                made[item.before] = Reentry(item.before, weights, dtype, device)
+            self.before.append(made.get(item.before))
         self.final_norm = build_norm(spec.final_norm, weights, dtype, device)
         self.lm_head = weights.device_tensor(spec.lm_head, dtype, device)   # the embedding itself when tied
         weights.release()
@@ -82,8 +90,16 @@ class DecoderModel:
         resid = ctx.workspace.buffer("residual", T, H, torch.float32)
         ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled,
                        scale=float(self.spec.embedding_scale))
+        x0 = None
+        if any(b is not None for b in self.before):
+            # the embedding's output, for the run items that mix it back into the stream
+            x0 = ctx.workspace.buffer("embedding_out", T, H, torch.float32)
+            ops.widen(x0, resid)
         delta = None
-        for item, cache in zip(self.spec.run_order, caches):
+        for item, cache, before in zip(self.spec.run_order, caches, self.before):
+            if before is not None:
+                before.forward(ctx, resid, delta, x0)
+                delta = None
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
         return resid, delta
 
@@ -97,8 +113,8 @@ class DecoderModel:
         if out is None:
             out = torch.empty((n_rows, V), dtype=torch.float32, device=self.device)
         out = linear(normed, self.lm_head, out)
-        if self.spec.logit_cap > 0:
-            ops.logit_cap(out, float(self.spec.logit_cap))
+        if self.spec.logit_cap > 0 or self.spec.logit_scale != 1.0:
+            ops.logit_cap(out, float(self.spec.logit_cap), float(self.spec.logit_scale))
         return out
 
     def forward(self, ctx: StepContext, caches: List[LayerCache], rows: torch.Tensor, n_rows: int,

@@ -53,6 +53,7 @@ MODULES: Dict[str, List[str]] = {
     "linear_attention": [],
     "latent_attention": [],
     "moe": [],
+    "recurrent": [],
     "runtime": [],      # host code only: cache manager, scheduler, step arrays
 }
 

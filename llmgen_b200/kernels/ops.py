@@ -105,12 +105,12 @@ def embed_rows(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, bad_fl
                                     _stream()))
 
 
-def logit_cap(logits: torch.Tensor, cap: float) -> None:
-    """logits (float32, contiguous) = cap * tanh(logits / cap), in place."""
+def logit_cap(logits: torch.Tensor, cap: float, scale: float = 1.0) -> None:
+    """logits (float32, contiguous) = scale * logits, then (cap > 0) cap * tanh(logits / cap), in place."""
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise KernelError("logit_cap: logits must be contiguous float32")
     lib = build.load("elementwise")
-    _check(lib, lib.llmk_logit_cap(_ptr(logits), c_longlong(logits.numel()), c_float(cap), _stream()))
+    _check(lib, lib.llmk_logit_cap(_ptr(logits), c_longlong(logits.numel()), c_float(scale), c_float(cap), _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,
@@ -195,13 +195,16 @@ def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor
               sin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
               nq: int, nk: int, hd: int, rot: int, page_size: int, eps: float,
               q_offset: float = 0.0, k_offset: float = 0.0, q_out: Optional[torch.Tensor] = None,
-              pairing: str = "half", head_norm: str = "rmsnorm") -> None:
+              pairing: str = "half", head_norm: str = "rmsnorm", bias: Optional[torch.Tensor] = None, vd: int = 0) -> None:
     """Per-head norm and rotary encoding of q and k, and the cache write of k, v.  `qkv` holds the
     packed rows [n, (nq + 2 nk) hd] as an array (q is then rewritten in place unless `q_out` is
     given) or as a `Partials` (q goes to `q_out`, which gives the storage dtype).  `pairing` says which
     values of a head the rotary encoding turns together and `head_norm` which norm runs over a head
-    (see `ROTARY_PAIRINGS`, `HEAD_NORMS`); the kernel refuses the ones it does not implement."""
+    (see `ROTARY_PAIRINGS`, `HEAD_NORMS`); the kernel refuses the ones it does not implement.  `bias` (float32 over the
+    packed columns) is added before the norms; `vd` is the width of a value head where it differs from `hd`."""
     lib = build.load("attn_prep")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != (nq + nk) * hd + nk * (vd or hd)):
+        raise KernelError("attn_prep: the bias is one float32 per packed column")
     nkv_cache = kcache.shape[1] if kcache is not None else 0
     splits, split_stride = 0, 0
     if isinstance(qkv, Partials):
@@ -223,7 +226,7 @@ def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor
                                    c_int(n), c_int(nq), c_int(nk), c_int(nkv_cache), c_int(hd), c_int(rot),
                                    c_int(page_size), c_float(eps), c_float(q_offset), c_float(k_offset),
                                    c_int(pairing_code(pairing)), c_int(head_norm_code(head_norm)),
-                                   c_int(dtype_code(dtype)), _stream()))
+                                   _ptr(bias), c_int(vd), c_int(dtype_code(dtype)), _stream()))
 
 
 # ------------------------------------------------------------------------- matrix products
@@ -528,11 +531,16 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                     block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
                     hd: int, page_size: int, window: int, scale: float, num_parts: int = 1, part_size: int = 0,
-                    scratch: Optional[torch.Tensor] = None) -> None:
-    """out[t, nq*hd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu)."""
+                    scratch: Optional[torch.Tensor] = None, vd: int = 0, softcap: float = 0.0, sink: bool = False,
+                    gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, nq*vd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu).  `vd`: the values' width where
+    it differs from `hd`; `softcap` > 0 bounds the scores by softcap * tanh(s / softcap); `sink` adds exp(0) to the
+    softmax's denominator; `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate)."""
     lib = build.load("attention")
+    if gate is not None and gate.dtype != q.dtype:
+        raise KernelError("paged_attention: the gate has the storage dtype")
     if num_parts > 1:
-        need = attention_scratch_floats(n_tokens, nq, hd, num_parts)
+        need = attention_scratch_floats(n_tokens, nq, vd or hd, num_parts)
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"paged_attention: split into {num_parts} parts needs {need} float32 of scratch")
     _check(lib, lib.llmk_paged_attention(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(q_stride),
@@ -540,7 +548,9 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(n_tiles),
                                          c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
-                                         _ptr(scratch), c_int(dtype_code(q.dtype)), _stream()),
+                                         _ptr(scratch), c_int(vd), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
+                                         c_longlong(_row_stride(gate) if gate is not None else 0),
+                                         c_int(dtype_code(q.dtype)), _stream()),
            2 if num_parts > 1 else 1)
 
 
@@ -665,7 +675,7 @@ def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, see
 
 
 # ---------------------------------------------------------------------- rows of post-norm layers
-ACTIVATIONS = {"relu2": 0, "clamped_glu": 1}
+ACTIVATIONS = {"relu2": 0, "clamped_glu": 1, "gelu_tanh_glu": 2}
 
 
 def _delta_args(y, dtype: torch.dtype):
@@ -703,7 +713,8 @@ def cast_rows(out: torch.Tensor, src: torch.Tensor) -> None:
 def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: float = 0.0) -> None:
     """out[n, F] = relu(x)^2 ("relu2", x [n, F]) or the clamped gated unit of x [n, 2F] ("clamped_glu": gate in
     the first F columns, up in the last): g' = min(g, limit), u' = clamp(u, -limit, limit),
-    out = g' sigmoid(alpha g') (u' + 1).  `x` is an array or a `Partials`."""
+    out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up of x [n, 2F] ("gelu_tanh_glu").  `x` is an array or a
+    `Partials`."""
     lib = build.load("rowwise")
     try:
         mode = ACTIVATIONS[activation]
@@ -729,6 +740,98 @@ def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight
         raise KernelError("gated_rmsnorm: o must be contiguous float32 and the gate of the storage dtype")
     _check(lib, lib.llmk_gated_rmsnorm(_ptr(out), _ptr(o), _ptr(gate), _ptr(weight), c_int(n), c_int(H), c_longlong(_row_stride(gate)),
                                        c_float(eps), c_int(dtype_code(out.dtype)), _stream()))
+
+
+def add_bias(y, bias: torch.Tensor) -> None:
+    """y[r, :] += bias (float32 [H]); y is an array [n, H] (bfloat16 or float32, rows any stride apart) or a `Partials`,
+    whose first slice takes the bias."""
+    lib = build.load("rowwise")
+    t = y.tensor[0] if isinstance(y, Partials) else y
+    if bias.dtype != torch.float32 or bias.numel() != t.shape[-1]:
+        raise KernelError("add_bias: one float32 per column")
+    _check(lib, lib.llmk_add_bias(_ptr(t), _ptr(bias), c_int(t.shape[0]), c_int(t.shape[1]), c_longlong(_row_stride(t)),
+                                  c_int(dtype_code(t.dtype)), _stream()))
+
+
+def concat_stream(out: torch.Tensor, resid: torch.Tensor, delta, x0: torch.Tensor) -> None:
+    """out[n, 2H] (storage dtype) = [resid + delta | x0]; resid and x0 float32 [n, H]; `delta` None, an array of the
+    storage dtype or a `Partials`."""
+    lib = build.load("rowwise")
+    n, H = resid.shape
+    if resid.dtype != torch.float32 or x0.dtype != torch.float32 or tuple(out.shape) != (n, 2 * H) or not out.is_contiguous():
+        raise KernelError("concat_stream: float32 [n, H] twice in, [n, 2H] out")
+    src, splits, stride = (None, 0, 0) if delta is None else _delta_args(delta, out.dtype)
+    _check(lib, lib.llmk_concat_stream(_ptr(out), _ptr(resid), _ptr(src), _ptr(x0), c_int(n), c_int(H), c_int(splits),
+                                       c_longlong(stride), c_int(dtype_code(out.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------------ recurrent mixers
+CONV_ACTIVATIONS = {"none": 0, "silu": 1}
+
+
+def short_conv(out: torch.Tensor, x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+               state_slots: torch.Tensor, n_seqs: int, in_bias: Optional[torch.Tensor] = None,
+               conv_bias: Optional[torch.Tensor] = None, activation: str = "none", update_state: bool = True) -> None:
+    """out[t, c] (float32) = act(sum_i taps[c, i] in(t - (K-1) + i, c) + conv_bias[c]) over each sequence of the step, in
+    = x + in_bias; a sequence's first tokens read the last K - 1 inputs of the step before from `state` [slots, >= (K-1) C]
+    (a view whose rows are the slots), which is then brought up to date (csrc/recurrent.cu)."""
+    lib = build.load("recurrent")
+    n, C = out.shape
+    K = taps.shape[1]
+    if out.dtype != torch.float32 or taps.dtype != torch.float32 or state.dtype != torch.float32 or tuple(taps.shape) != (C, K):
+        raise KernelError("short_conv: out, taps [channels, K] and state are float32")
+    if x.shape[0] != n or x.shape[1] != C or state.shape[1] < (K - 1) * C:
+        raise KernelError("short_conv: shapes do not fit")
+    _check(lib, lib.llmk_short_conv(_ptr(out), c_longlong(_row_stride(out)), _ptr(x), c_longlong(_row_stride(x)), _ptr(in_bias),
+                                    _ptr(taps), _ptr(conv_bias), _ptr(state), c_longlong(_row_stride(state)), _ptr(cu_q),
+                                    _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(C), c_int(K),
+                                    c_int(CONV_ACTIVATIONS[activation]), c_int(1 if update_state else 0),
+                                    c_int(dtype_code(x.dtype)), _stream()),
+           2 if update_state and K > 1 else 1)
+
+
+def rglru(out: torch.Tensor, scratch: torch.Tensor, u: torch.Tensor, w_a: torch.Tensor, w_i: torch.Tensor,
+          b_a: Optional[torch.Tensor], b_i: Optional[torch.Tensor], lam: torch.Tensor, y: torch.Tensor,
+          y_bias: Optional[torch.Tensor], state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
+          blocks: int, decay_scale: float) -> None:
+    """The real-gated linear recurrent unit over each sequence's new tokens (csrc/recurrent.cu): gates from u (float32
+    [n, C], the convolution's output) by the block-diagonal matrices w_a, w_i [blocks, C/blocks, C/blocks], then
+    S = a S + sqrt(1 - a^2) i u from `state` [slots, >= C] and out[n, C] (storage dtype) = S * gelu_tanh(y + y_bias).
+    `scratch`: float32 [2, n, C]."""
+    lib = build.load("recurrent")
+    n, C = u.shape
+    if u.dtype != torch.float32 or not u.is_contiguous() or scratch.dtype != torch.float32 or scratch.numel() < 2 * n * C:
+        raise KernelError("rglru: u and the scratch [2, n, C] are contiguous float32")
+    if w_a.dtype != out.dtype or w_i.dtype != out.dtype or y.dtype != out.dtype or not w_a.is_contiguous() or not w_i.is_contiguous():
+        raise KernelError("rglru: gate matrices, y and out share the storage dtype")
+    if tuple(w_a.shape) != (blocks, C // blocks, C // blocks) or w_i.shape != w_a.shape or state.shape[1] < C:
+        raise KernelError("rglru: shapes do not fit")
+    flat = scratch.view(-1)
+    _check(lib, lib.llmk_rglru(_ptr(out), c_longlong(_row_stride(out)), _ptr(flat), c_void_p(flat.data_ptr() + 4 * n * C), _ptr(u),
+                               _ptr(w_a), _ptr(w_i), _ptr(b_a), _ptr(b_i), _ptr(lam), _ptr(y), c_longlong(_row_stride(y)),
+                               _ptr(y_bias), _ptr(state), c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots),
+                               c_int(n_seqs), c_int(n), c_int(C), c_int(blocks), c_float(decay_scale),
+                               c_int(dtype_code(out.dtype)), _stream()), 2)
+
+
+def delta_scan(out: torch.Tensor, qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
+               heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float, q_scale: float) -> None:
+    """The gated delta rule with a decay per key channel over each sequence's new tokens (csrc/recurrent.cu).  qkv float32
+    [n, 2 kv_heads dim + heads vdim] (after convolution and silu); beta [n, heads] (storage dtype, any row stride, before
+    its sigmoid); decay float32 [n, heads dim] (before dt_bias and softplus); state [slots, >= heads dim vdim] float32;
+    out float32 [n, heads vdim]."""
+    lib = build.load("recurrent")
+    n = out.shape[0]
+    if out.dtype != torch.float32 or qkv.dtype != torch.float32 or decay.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("delta_scan: out, qkv, decay and state are float32")
+    if not out.is_contiguous() or not decay.is_contiguous() or out.shape[1] != heads * vdim or decay.shape[1] != heads * dim \
+            or qkv.shape[1] != 2 * kv_heads * dim + heads * vdim or state.shape[1] < heads * dim * vdim:
+        raise KernelError("delta_scan: shapes do not fit")
+    _check(lib, lib.llmk_delta_scan(_ptr(out), _ptr(qkv), c_longlong(_row_stride(qkv)), _ptr(beta), c_longlong(_row_stride(beta)),
+                                    _ptr(decay), _ptr(dt_bias), _ptr(a_log), _ptr(state), c_longlong(_row_stride(state)),
+                                    _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(heads), c_int(kv_heads), c_int(dim),
+                                    c_int(vdim), c_float(unit_eps), c_float(q_scale), c_int(dtype_code(beta.dtype)), _stream()))
 
 
 # ------------------------------------------------------------------------------ linear attention

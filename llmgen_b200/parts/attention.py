@@ -51,7 +51,13 @@ class GQAAttention(Mixer):
 
     Order and formulas: src/models/qwen3.zig:192-207 (q/k norm before RoPE, norm weights
     shared by all heads), src/module/attention.zig:85-92, src/backend/cpu/attention.zig:64-118.
-    A run item with `writes=False` projects q only and reads the cache another item wrote."""
+    A run item with `writes=False` projects q only and reads the cache another item wrote.
+
+    Variations (`AttentionSpec`): biases on the projections, values of another width than keys, a bound on the scores
+    (softcap), a sink in the softmax's denominator and an output gate.  The gate's matrix is packed behind q, k and v,
+    the biases of q, k and v are added by the preparation kernel before the per-head norms, and bound, sink and gate
+    are applied inside the general attention kernel (csrc/attention.cu), which takes every step of a layer that has
+    any of them; the output projection's bias is added to its result (or to the first of its slices)."""
 
     # what `prepare_step` adds depends on the lengths of the step's portions only, not on their
     # positions or requests: the engine may keep it across decode steps of one batch size
@@ -64,8 +70,14 @@ class GQAAttention(Mixer):
     @staticmethod
     def weight_decls(spec: AttentionSpec):
         qd, kd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        vd, od = spec.num_kv_heads * spec.value_dim, spec.num_heads * spec.value_dim
         decls = [WeightDecl(spec.q_proj, (qd, spec.hidden_size)), WeightDecl(spec.k_proj, (kd, spec.hidden_size)),
-                 WeightDecl(spec.v_proj, (kd, spec.hidden_size)), WeightDecl(spec.o_proj, (spec.hidden_size, qd))]
+                 WeightDecl(spec.v_proj, (vd, spec.hidden_size)), WeightDecl(spec.o_proj, (spec.hidden_size, od))]
+        for name, width in ((spec.q_bias, qd), (spec.k_bias, kd), (spec.v_bias, vd), (spec.o_bias, spec.hidden_size)):
+            if name:
+                decls.append(WeightDecl(name, (width,), VECTOR))
+        if spec.gate_proj:
+            decls.append(WeightDecl(spec.gate_proj, (od, spec.hidden_size)))
         for n in (spec.q_norm, spec.k_norm):
             if n is not None:
                 decls += norm_class(n).weight_decls(n)
@@ -73,7 +85,15 @@ class GQAAttention(Mixer):
 
     @staticmethod
     def kernel_modules(spec):
+        if GQAAttention.varied(spec):
+            return ("attn_prep", "attention", "rowwise") + GEMM_MODULES
         return ("attn_prep", "attention", "attention_decode", "attention_tc") + GEMM_MODULES
+
+    @staticmethod
+    def varied(spec: AttentionSpec) -> bool:
+        """True for a layer that only the general kernels take (see the class's last paragraph)."""
+        return bool(spec.q_bias or spec.k_bias or spec.v_bias or spec.o_bias or spec.gate_proj or spec.sink or spec.softcap > 0
+                    or spec.value_dim != spec.head_dim)
 
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
         if spec.num_heads % spec.num_kv_heads != 0:
@@ -85,11 +105,25 @@ class GQAAttention(Mixer):
                 raise ValueError(f"attention: per-head norms must run over head_dim and be one of {sorted(ops.HEAD_NORMS)}")
         self.spec = spec
         self.dtype = dtype
-        self.nq, self.nkv, self.hd = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.nq, self.nkv, self.hd, self.vd = spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim
+        if self.vd % 8 != 0 or self.vd > 512:
+            raise ValueError(f"attention: the values' width {self.vd} must be a multiple of 8, at most 512")
+        self.is_varied = self.varied(spec)
         # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
-        self.w_qkv = torch.cat([weights.device_tensor(n, dtype, device, keep=False) for n in (spec.q_proj, spec.k_proj, spec.v_proj)],
-                               dim=0).contiguous()
+        names = [spec.q_proj, spec.k_proj, spec.v_proj] + ([spec.gate_proj] if spec.gate_proj else [])
+        self.w_qkv = torch.cat([weights.device_tensor(n, dtype, device, keep=False) for n in names], dim=0).contiguous()
         self.w_q = self.w_qkv[: self.nq * self.hd]
+        self.gate_off = (self.nq + self.nkv) * self.hd + self.nkv * self.vd if spec.gate_proj else -1
+        # a run item that reads another item's cache projects q (and the gate) only
+        self.w_q_gate = (torch.cat([self.w_q, self.w_qkv[self.gate_off:]], dim=0).contiguous() if spec.gate_proj else self.w_q)
+        self.bias = None
+        if spec.q_bias or spec.k_bias or spec.v_bias:
+            widths = (self.nq * self.hd, self.nkv * self.hd, self.nkv * self.vd)
+            self.bias = torch.cat([weights.device_tensor(n, dtype, device, keep=False) if n else
+                                   torch.zeros(w, dtype=torch.float32, device=device)
+                                   for n, w in zip((spec.q_bias, spec.k_bias, spec.v_bias), widths)]).contiguous()
+        self.o_bias = weights.device_tensor(spec.o_bias, dtype, device) if spec.o_bias else None
+        self.softcap, self.sink = float(spec.softcap), bool(spec.sink)
         self.w_o = weights.device_tensor(spec.o_proj, dtype, device)
         self.q_gain = weights.device_tensor(spec.q_norm.weight, dtype, device) if spec.q_norm else None
         self.k_gain = weights.device_tensor(spec.k_norm.weight, dtype, device) if spec.k_norm else None
@@ -111,7 +145,8 @@ class GQAAttention(Mixer):
 
     # -- what the engine asks
     def cache_request(self) -> KVRequest:
-        return KVRequest(WINDOW if self.window else FULL, self.window, self.nkv, self.hd)
+        return KVRequest(WINDOW if self.window else FULL, self.window, self.nkv, self.hd,
+                         v_head_dim=self.vd if self.vd != self.hd else 0)
 
     def max_positions(self):
         return self.position.max_positions if self.position is not None else None
@@ -120,7 +155,7 @@ class GQAAttention(Mixer):
         add_query_tiles(builder, bq, self.window, heaviest_first)
 
     def tc_tile_queries(self, page_size: int) -> int:
-        if self.dtype != torch.bfloat16:
+        if self.dtype != torch.bfloat16 or self.is_varied:
             return 0
         if page_size not in self._tc_bq:
             self._tc_bq[page_size] = ops.attention_tc_tile_queries(self.nq, self.nkv, self.hd, page_size)
@@ -128,7 +163,7 @@ class GQAAttention(Mixer):
 
     def step_arrays_key(self):
         """Mixers with equal keys add the same arrays in `prepare_step`: the engine asks one of them."""
-        return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, str(self.dtype))
+        return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, str(self.dtype), self.is_varied)
 
     def prepare_step(self, builder) -> None:
         """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step will
@@ -142,7 +177,9 @@ class GQAAttention(Mixer):
 
     def _split(self, ctx):
         """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""
-        if not ctx.pure_decode:
+        if not ctx.pure_decode or self.is_varied:
+            # (a layer with a bound, a sink or a gate: one part, so that a token's logits do not depend on whether
+            # it was decoded alone or beside a portion)
             return 1, 0
         G = self.nq // self.nkv
         chunks = (G + 15) // 16
@@ -163,8 +200,8 @@ class GQAAttention(Mixer):
         """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed projection
         (and the float32 slices of two products cut along K), q, the attention's output and the output projection."""
         elem = 2 if self.dtype == torch.bfloat16 else 4
-        packed = (self.nq + 2 * self.nkv) * self.hd
-        return tokens * (packed + 2 * self.nq * self.hd + self.spec.hidden_size) * elem + 2 * ops.SLICED_PRODUCT_BYTES
+        packed = self.w_qkv.shape[0]
+        return tokens * (packed + 2 * self.nq * max(self.hd, self.vd) + self.spec.hidden_size) * elem + 2 * ops.SLICED_PRODUCT_BYTES
 
     def forward(self, ctx, x, cache: LayerCache):
         T = ctx.n_tokens
@@ -173,6 +210,8 @@ class GQAAttention(Mixer):
         nk = self.nkv if cache.writes else 0
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
+        if self.is_varied:
+            return self._forward_varied(ctx, x, cache, group, nk, cos, sin, rot)
         decode = (self.dtype == torch.bfloat16 and ctx.pure_decode
                   and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size))
         fused = decode and ops.attention_decode_fuses_prep(self.hd, rot)
@@ -220,6 +259,32 @@ class GQAAttention(Mixer):
                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
                             self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch)
         return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+
+    def _forward_varied(self, ctx, x, cache, group, nk, cos, sin, rot):
+        """A layer with biases, another value width, a bound on the scores, a sink or a gate: the packed projection as
+        an array (the gate's columns are read from it as they are), the general preparation and attention kernels."""
+        T, ws = ctx.n_tokens, ctx.workspace
+        w = self.w_qkv if cache.writes else self.w_q_gate
+        packed = linear(x, w, ws.buffer("attn_qkvg" if cache.writes else "attn_qg", T, w.shape[0], self.dtype))
+        gate = None
+        if self.gate_off >= 0:
+            gate = packed[:, self.gate_off:] if cache.writes else packed[:, self.nq * self.hd:]
+        bias = self.bias if (self.bias is None or cache.writes) else self.bias[: self.nq * self.hd]
+        q = ws.buffer("attn_q", T, self.nq * self.hd, self.dtype)
+        ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
+                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q,
+                      pairing=self.pairing, head_norm=self.head_norm, bias=bias, vd=self.vd)
+        o = ws.buffer("attn_o", T, self.nq * self.vd, self.dtype)
+        tile_seq = ctx.array(self.tiles_name + "_seq")
+        tile_q0 = ctx.array(self.tiles_name + "_q0")
+        ops.paged_attention(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
+                            ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
+                            self.hd, cache.page_size, self.window, float(self.spec.scale), 1, 0, None,
+                            vd=self.vd, softcap=self.softcap, sink=self.sink, gate=gate)
+        out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+        if self.o_bias is not None:
+            ops.add_bias(out, self.o_bias)
+        return out
 
     def _decode(self, ctx, o, q, cache, group, scale, prep=None) -> None:
         """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part; the

@@ -21,24 +21,26 @@ class PreNormBlock(Part):
 
     @staticmethod
     def weight_decls(spec: PreNormBlockSpec):
-        return (norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm)
-                + mixer_class(spec.mixer).weight_decls(spec.mixer)
-                + norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm)
-                + feed_forward_class(spec.ffn).weight_decls(spec.ffn))
+        decls = norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm) + mixer_class(spec.mixer).weight_decls(spec.mixer)
+        if spec.ffn is not None:
+            decls = decls + norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm) + feed_forward_class(spec.ffn).weight_decls(spec.ffn)
+        return decls
 
     @staticmethod
     def kernel_modules(spec: PreNormBlockSpec):
-        return (tuple(norm_class(spec.mixer_norm).kernel_modules(spec.mixer_norm))
-                + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer))
-                + tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn)))
+        mods = (tuple(norm_class(spec.mixer_norm).kernel_modules(spec.mixer_norm))
+                + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer)))
+        if spec.ffn is not None:
+            mods += tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn))
+        return mods
 
     def __init__(self, spec: PreNormBlockSpec, weights, dtype, device):
         self.spec = spec
         self.dtype = dtype
         self.mixer_norm = build_norm(spec.mixer_norm, weights, dtype, device)
         self.mixer = build_mixer(spec.mixer, weights, dtype, device)
-        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device)
-        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device)
+        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device) if spec.ffn is not None else None
+        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device) if spec.ffn is not None else None
 
     def workspace_bytes(self, tokens: int) -> int:
         """Bytes of activations a step of `tokens` rows keeps in the workspace for this layer: the normed
@@ -46,13 +48,15 @@ class PreNormBlock(Part):
         counts as nothing and must allocate before any graph is captured, like every part)."""
         elem = 2 if self.dtype == torch.bfloat16 else 4
         own = tokens * self.spec.mixer_norm.dim * elem
-        parts = [getattr(p, "workspace_bytes", None) for p in (self.mixer, self.ffn)]
+        parts = [getattr(p, "workspace_bytes", None) for p in (self.mixer, self.ffn) if p is not None]
         return own + max([f(tokens) for f in parts if f is not None] or [0])
 
     def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
         T, H = resid.shape
         x = self.mixer_norm.add_norm(resid, delta, ctx.workspace.buffer("block_normed", T, H, self.dtype))
         mixed = self.mixer.forward(ctx, x, cache)
+        if self.ffn is None:
+            return mixed          # a layer without a feed-forward: the next norm adds the mixer's output
         x = self.ffn_norm.add_norm(resid, mixed, ctx.workspace.buffer("block_normed", T, H, self.dtype))
         return self.ffn.forward(ctx, x)
 

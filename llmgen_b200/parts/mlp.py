@@ -39,18 +39,20 @@ class GatedMLP(FeedForward):
 
     @staticmethod
     def kernel_modules(spec):
-        return ("elementwise",) + GEMM_MODULES
+        return ("elementwise", "rowwise") + GEMM_MODULES
 
     def __init__(self, spec: GatedMLPSpec, weights, dtype, device):
-        if spec.activation != "silu":
+        if spec.activation not in ("silu", "gelu_tanh"):
             raise ValueError(f"gated feed-forward: activation {spec.activation!r} is not supported")
         self.spec = spec
         self.dtype = dtype
         F = spec.intermediate_size
+        # the products' gated epilogues apply silu; another activation runs as a pass over the packed product
+        self.silu = spec.activation == "silu"
         # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
         w_gate = weights.device_tensor(spec.gate_proj, dtype, device, keep=False)
         w_up = weights.device_tensor(spec.up_proj, dtype, device, keep=False)
-        if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0:
+        if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0 and self.silu:
             self.group = GATE_UP_GROUP
             packed = interleave_gate_up(w_gate, w_up)
         else:
@@ -71,6 +73,10 @@ class GatedMLP(FeedForward):
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
         act = ws.buffer("ffn_act", T, F, self.dtype)
+        if not self.silu:
+            gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
+            ops.act_rows(act, gate_up, "gelu_tanh_glu")
+            return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
         cluster = min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) if gated and T <= ops.SKINNY_CLUSTER_MAX_ROWS else 1
         if gated and T <= ops.ROWS8_GATED_BEST_ROWS and ops.gemm_rows8_gated_usable(x, self.w_gate_up):

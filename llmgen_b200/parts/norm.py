@@ -8,7 +8,7 @@ import torch
 from ..kernels import ops
 from .base import Part
 from .registry import register_norm
-from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, RMSNormSpec, WeightDecl
+from .spec import INIT_NORMAL, INIT_ONE_PLUS_NORMAL, VECTOR, RMSNormSpec, WeightDecl
 
 
 class RMSNorm(Part):
@@ -19,7 +19,8 @@ class RMSNorm(Part):
 
     @staticmethod
     def weight_decls(spec: RMSNormSpec):
-        return [WeightDecl(spec.weight, (spec.dim,), VECTOR, INIT_ONE_PLUS_NORMAL)]
+        # a gain stored around zero (the kernel adds `weight_offset`) is drawn around zero in the random-weights mode
+        return [WeightDecl(spec.weight, (spec.dim,), VECTOR, INIT_ONE_PLUS_NORMAL if spec.weight_offset == 0.0 else INIT_NORMAL)]
 
     @staticmethod
     def kernel_modules(spec):

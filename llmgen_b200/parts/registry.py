@@ -107,6 +107,13 @@ def model_weight_decls(model_spec) -> List[WeightDecl]:
     decls = [WeightDecl(model_spec.embedding, (model_spec.vocab_size, model_spec.hidden_size))]
     for layer in model_spec.layers:
         decls += block_class(layer).weight_decls(layer)
+    from .reentry import Reentry
+    seen = set()
+    for item in model_spec.run_order:
+        before = getattr(item, "before", None)
+        if before is not None and (before.proj, before.table) not in seen:
+            seen.add((before.proj, before.table))
+            decls += Reentry.weight_decls(before, model_spec.hidden_size)
     decls += norm_class(model_spec.final_norm).weight_decls(model_spec.final_norm)
     if not model_spec.tied:
         decls.append(WeightDecl(model_spec.lm_head, (model_spec.vocab_size, model_spec.hidden_size)))
@@ -119,6 +126,9 @@ def model_kernel_modules(model_spec) -> List[str]:
     mods = ["elementwise", "gemm_simt", "gemv", "gemm_tc", "sampling"]
     for layer in model_spec.layers:
         mods += list(block_class(layer).kernel_modules(layer))
+    if any(getattr(item, "before", None) is not None for item in model_spec.run_order):
+        from .reentry import Reentry
+        mods += list(Reentry.kernel_modules(None))
     return list(dict.fromkeys(mods))
 
 
@@ -129,4 +139,5 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from . import attention, block, latent_attention, linear_attention, mlp, moe, norm, rope  # noqa: F401
+        from . import (attention, block, gated_delta, latent_attention, linear_attention, mlp, moe, norm,  # noqa: F401
+                       rglru, rope)

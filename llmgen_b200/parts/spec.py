@@ -90,7 +90,24 @@ class AttentionSpec:
     k_norm: Optional[RMSNormSpec] = None
     position: Optional[RopeSpec] = None
     window: Optional[int] = None
+    # Variations, all off by default.  `v_head_dim`: width of a value head where it differs from a key's.
+    # `q_bias` .. `o_bias`: names of bias vectors added in the projections.  `softcap` > 0: the scaled score s
+    # becomes softcap * tanh(s / softcap).  `sink`: the softmax's denominator has one more term exp(0), a key of
+    # score 0 without a value, so the weights of a row sum to less than one.  `gate_proj`: the heads side by side
+    # are multiplied by sigmoid(x Wg^T) before the output projection.
+    v_head_dim: Optional[int] = None
+    q_bias: Optional[str] = None
+    k_bias: Optional[str] = None
+    v_bias: Optional[str] = None
+    o_bias: Optional[str] = None
+    softcap: float = 0.0
+    sink: bool = False
+    gate_proj: Optional[str] = None
     kind: str = "attention"
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -151,6 +168,80 @@ class LatentAttentionSpec:
     kind: str = "latent_attention"
 
 
+@dataclass(frozen=True)
+class ShortConvSpec:
+    """A causal convolution over time on each channel by itself: out_t = sum_j taps[:, j] in_(t - (K-1) + j) + bias,
+    taps [channels, K] with the last column on the current token, zeros before the first token of a sequence.  The last
+    K - 1 inputs of a sequence are part of its mixer's state."""
+    channels: int
+    taps: int
+    weight: str
+    bias: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class RGLRUSpec:
+    """A recurrent block around a real-gated linear recurrent unit.
+
+    Two branches of `width` channels off the mixer's input: y = gelu_tanh(x Wy^T + by) and u = conv(x Wx^T + bx).
+    The channels are cut into `blocks` equal parts; in part b, r = sigmoid(Ra_b u_b + ba_b) and i = sigmoid(Ri_b u_b + bi_b)
+    with square matrices per part.  a = exp(-decay_scale * r * softplus(lam)), S_t = a S_(t-1) + sqrt(1 - a^2) (i u),
+    S float32 and zero before the first token; output (S * y) Wo^T.  State per request: S and the convolution's last
+    taps - 1 inputs."""
+    hidden_size: int
+    width: int
+    blocks: int
+    conv: ShortConvSpec
+    y_proj: str
+    x_proj: str
+    o_proj: str
+    a_gate: str                          # [blocks, n, n], n = width / blocks
+    i_gate: str
+    lam: str                             # [width]
+    y_bias: Optional[str] = None
+    x_bias: Optional[str] = None
+    a_gate_bias: Optional[str] = None    # [blocks, n]
+    i_gate_bias: Optional[str] = None
+    decay_scale: float = 8.0
+    kind: str = "rglru"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule with a decay per head and key channel, state carried from token to token.
+
+    q, k [kv_heads, key_dim] and v [heads, value_dim] are projections that pass a short convolution (one spec over
+    the channels of q, k and v side by side) and silu; q and k are then unit vectors per head, x / sqrt(sum x^2 + unit_eps),
+    and q is multiplied by key_dim^(-1/2).  Head h reads q/k head h // (heads / kv_heads).  beta = sigmoid(x Wb^T) per head.
+    g = exp(-exp(A_log_h) * softplus(x Wa1^T Wa2^T + dt_bias)) [heads, key_dim].  Per head, S [key_dim, value_dim] float32,
+    zero before the first token:  S <- diag(g) S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q.
+    Each head's o passes an RMSNorm over value_dim (`out_norm`, one gain vector for all heads), is multiplied by
+    sigmoid(x Wg1^T Wg2^T) and projected by Wo.  State per request: S and the convolution's last taps - 1 inputs."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv: ShortConvSpec                  # channels = 2 kv_heads key_dim + heads value_dim
+    conv_weights: Tuple[str, ...]        # the taps of q, k and v, stacked into `conv` when the model is loaded
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    beta_proj: str
+    decay_down: str                      # Wa1 [rank, hidden]
+    decay_up: str                        # Wa2 [heads key_dim, rank]
+    decay_bias: str                      # dt_bias [heads key_dim]
+    decay_log: str                       # A_log [heads]
+    gate_down: str                       # Wg1
+    gate_up: str                         # Wg2 [heads value_dim, rank]
+    o_proj: str
+    out_norm: RMSNormSpec
+    decay_rank: int = 0
+    gate_rank: int = 0
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
+
+
 # ---------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class DenseMLPSpec:
@@ -203,21 +294,22 @@ class GatedMLPSpec:
     gate_proj: str
     up_proj: str
     down_proj: str
-    activation: str = "silu"
+    activation: str = "silu"             # "silu" or "gelu_tanh"
     kind: str = "gated_mlp"
 
 
 # ----------------------------------------------------------------------------- blocks
 @dataclass(frozen=True)
 class PreNormBlockSpec:
-    """x1 = x + mixer(norm(x)); x2 = x1 + ffn(norm(x1)).
+    """x1 = x + mixer(norm(x)); x2 = x1 + ffn(norm(x1)).  `ffn` (and `ffn_norm`) may be None: a layer without a
+    feed-forward stops after the first sum.
 
     Reference: src/models/qwen3.zig:211-237.
     """
     mixer_norm: object
     mixer: object
-    ffn_norm: object
-    ffn: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
     kind: str = "prenorm"
 
 
@@ -233,16 +325,29 @@ class PostNormBlockSpec:
 
 
 @dataclass(frozen=True)
+class ReentrySpec:
+    """What happens to the residual stream before a run item: x <- [x | x0] W^T + table[row], with x0 the embedding's
+    output of the same token, W [hidden, 2 hidden] (the stream's columns first) and `table` [rows, hidden]."""
+    proj: str
+    table: str
+    row: int
+    rows: int
+    kind: str = "reentry"
+
+
+@dataclass(frozen=True)
 class RunItem:
     """One entry of the run list: run `layer`, with cache number `cache`.
 
     A layer may be named by several items (each with a cache of its own or a shared one),
     and an item with `writes_cache=False` reads the cache that another item filled in the
-    same step.  `cache` is None for a layer that keeps nothing between steps.
+    same step.  `cache` is None for a layer that keeps nothing between steps.  `before`: a `ReentrySpec`
+    applied to the residual stream before the layer runs.
     """
     layer: int
     cache: Optional[int]
     writes_cache: bool = True
+    before: Optional[ReentrySpec] = None
 
 
 @dataclass(frozen=True)
@@ -262,6 +367,7 @@ class ModelSpec:
     init_sigma_norm: float = 0.1
     embedding_scale: float = 1.0         # rows of the table are multiplied by this as they enter the residual
     logit_cap: float = 0.0               # > 0: logits = cap * tanh(logits / cap)
+    logit_scale: float = 1.0             # logits are multiplied by this (before the cap)
     # Tensors that a model folder of this architecture may carry although the model reads none of them
     # (shell patterns), and (name, declared name) pairs of such tensors that must then hold the same values.
     ignorable_tensors: Tuple[str, ...] = ()

@@ -63,8 +63,21 @@ def config_from_dict(data: dict, where: str = "config.json"):
 
 
 def config_from_folder(model_dir: str):
+    """(architecture entry, typed config) of a model folder.  A configuration class whose sizes are not all keys of its
+    config.json offers `fill_from_tensor_shapes(data, shapes) -> data`: it is then given the shapes of the folder's
+    tensors (the file's header is read, no tensor) and adds the sizes it finds there."""
     data = read_config_json(model_dir)
-    return config_from_dict(data, where=f"{model_dir}/config.json")
+    arch = resolve(architecture_name(data, f"{model_dir}/config.json"))
+    fill = getattr(arch.config_cls, "fill_from_tensor_shapes", None)
+    if fill is not None:
+        from .weights.safetensors_io import SafetensorsError, TensorDirectory
+        try:
+            directory = TensorDirectory(model_dir)
+            shapes = {name: tuple(directory.entry(name).shape) for name in directory.names()}
+        except SafetensorsError as e:
+            raise ConfigError(str(e)) from None
+        data = fill(data, shapes)
+    return arch, arch.config_cls.from_dict(data, f"{model_dir}/config.json")
 
 
 _builtin_loaded = False
