@@ -128,7 +128,9 @@ LLMK_EXPORT int llmk_short_conv(float* out, long long out_ld, const void* x, lon
 
 // ------------------------------------------------------------------------------------------------ RG-LRU
 // Block (tile of `GATE_OUT` outputs, block of channels b, tile of TT tokens): r = sigmoid(Ra_b u_b + ba), i = sigmoid(Ri_b u_b + bi),
-// log a = -scale r softplus(lam), a = exp(log a), b = sqrt(1 - a^2) i u  (1 - a^2 as -expm1(2 log a): no cancellation near a = 1).
+// log a = -scale r softplus(lam), a = exp(log a), b = sqrt(1 - a^2) i u.  What leaves is c = 1 - a = -expm1(log a), not a: many
+// a lie just below 1, where a float holds 1 - a to a few digits only and an exponential's last-bit error, always on the
+// same side, would add up over the thousands of tokens such a channel remembers; 1 - a^2 = c (2 - c) without cancellation.
 constexpr int GATE_OUT = 128;
 
 template <typename T, int TT>
@@ -192,12 +194,14 @@ __global__ void __launch_bounds__(GATE_OUT) rglru_gates_kernel(float* __restrict
         const float r = sigmoidf_(accA[tt] + bias_a);
         const float ig = sigmoidf_(accI[tt] + bias_i);
         const float loga = -decay_scale * r * sp;
-        a_out[(size_t)t * C + c] = expf(loga);
-        b_out[(size_t)t * C + c] = sqrtf(-expm1f(2.0f * loga)) * ig * Us[tt * n + o];
+        const float om = -expm1f(loga);
+        a_out[(size_t)t * C + c] = om;
+        b_out[(size_t)t * C + c] = sqrtf(om * (2.0f - om)) * ig * Us[tt * n + o];
     }
 }
 
-// Thread (sequence, channel): S = a S + b over the sequence's new tokens, out = S * gelu_tanh(y + y_bias).
+// Thread (sequence, channel): S = a S + b = (S - c S) + b over the sequence's new tokens (c = 1 - a, see above),
+// out = S * gelu_tanh(y + y_bias).
 template <typename T>
 __global__ void rglru_scan_kernel(T* __restrict__ out, long long out_ld, const float* __restrict__ a, const float* __restrict__ bx,
                                   const T* __restrict__ y, long long y_ld, const float* __restrict__ y_bias,
@@ -224,12 +228,12 @@ __global__ void rglru_scan_kernel(T* __restrict__ out, long long out_ld, const f
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            S = fmaf(av[i], S, bv[i]);
+            S = fmaf(-av[i], S, S) + bv[i];
             out[(size_t)(t + i) * out_ld + c] = from_float<T>(S * gelu_tanhf_(yv[i] + yb));
         }
     }
     for (; t < q_end; ++t) {
-        S = fmaf(a[(size_t)t * C + c], S, bx[(size_t)t * C + c]);
+        S = fmaf(-a[(size_t)t * C + c], S, S) + bx[(size_t)t * C + c];
         out[(size_t)t * out_ld + c] = from_float<T>(S * gelu_tanhf_(to_float(y[(size_t)t * y_ld + c]) + yb));
     }
     if (slot >= 0) state[(size_t)slot * state_ld + c] = S;
@@ -352,12 +356,12 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
         __syncthreads();      // the chunk before is consumed
         for (int idx = threadIdx.x; idx < DELTA_CHUNK * DP; idx += 256) {
             const int tt = idx / DP, d = idx % DP;
-            float qv = 0.f, kv = 0.f, gv = 1.f;
+            float qv = 0.f, kv = 0.f, gv = 0.f;      // gv: 1 - g (a decay just below 1 is held exactly enough only so)
             if (tt < nc && d < D) {
                 const size_t t = (size_t)(q_beg + c0 + tt);
                 qv = p.qkv[t * p.qkv_ld + (size_t)kvh * D + d];
                 kv = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
-                gv = expf(neg_exp_a * softplusf_(p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d] + p.dt_bias[(size_t)h * D + d]));
+                gv = -expm1f(neg_exp_a * softplusf_(p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d] + p.dt_bias[(size_t)h * D + d]));
             }
             qs[idx] = qv;
             ks[idx] = kv;
@@ -392,7 +396,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
             float kS = 0.f;
 #pragma unroll
             for (int i = 0; i < DSL; ++i) {
-                S[i] *= gr[4 * i];
+                S[i] = fmaf(-gr[4 * i], S[i], S[i]);
                 kS = fmaf(kr[4 * i], S[i], kS);
             }
             kS += __shfl_xor_sync(0xffffffffu, kS, 1);
