@@ -1,7 +1,10 @@
-"""`bench.py --designs`: Derupel beside Qwen3 at equal layer sizes, random weights, one B200.
+"""`bench.py --designs`: Derupel (or, with `--designs-family sarulix`, Sarulix) beside Qwen3 at equal layer sizes, random
+weights, one B200.
 
-For each size two models are built: a Derupel whose layers alternate its two mixers and its two feed-forwards, and the
-Qwen3 of the same width, depth, feed-forward width and vocabulary.  Measured for both:
+For each size two models are built: a Derupel whose layers alternate its two mixers and its two feed-forwards (a Sarulix
+whose four layers are a recurrent unit, the delta rule, attention and a recurrent unit again, each with a feed-forward,
+entered once through its loop's mixing step), and the Qwen3 of the same width, depth, feed-forward width and vocabulary.
+Measured for both:
 
   prefill   one prompt of 2,048 tokens through one step (the graph of its shape replayed), tokens/s and ms
   decode    steps of 8 single tokens at contexts from 512 upward through the decode graphs, tokens/s and ms a step
@@ -41,6 +44,22 @@ def derupel_config(s: dict) -> dict:
                        "mlp": dense if (i // 2) % 2 == 0 else moe})
     return {"architecture": "Derupel", "vocab": VOCAB, "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
             "layers": layers, "max_positions": CONTEXT}
+
+
+def sarulix_config(s: dict) -> dict:
+    W, heads, hd = s["width"], s["heads"], s["hd"]
+    dense = {"kind": "dense", "ff": s["ff"]}
+    lru = {"type": "rglru", "mixer": {"width": W, "blocks": heads, "conv": 4}, "mlp": dense}
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": hd, "vdim": hd, "conv": 4,
+                                                "decay_rank": 64, "gate_rank": 64}, "mlp": dense}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "softcap": 30.0, "rot": {"base": 10000.0, "dims": hd // 2}}, "mlp": dense}
+    layers = [lru, delta, att, lru][: s["layers"]] + [lru] * max(0, s["layers"] - 4)
+    return {"architecture": "Sarulix", "vocab": VOCAB, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_scale": 1.0, "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers, "max_positions": CONTEXT}
+
+
+FAMILIES = {"derupel": derupel_config, "sarulix": sarulix_config}
 
 
 def qwen3_config(s: dict) -> dict:
@@ -160,7 +179,8 @@ def run(args, root: str, sampler=None) -> dict:
     w0 = sampler.mark() if sampler is not None else None
     for name in wanted:
         entry = {}
-        for design, cfg in (("derupel", derupel_config(SIZES[name])), ("qwen3", qwen3_config(SIZES[name]))):
+        family = getattr(args, "designs_family", "") or "derupel"
+        for design, cfg in ((family, FAMILIES[family](SIZES[name])), ("qwen3", qwen3_config(SIZES[name]))):
             model = random_model(cfg, 2, "bfloat16", init_on_device=True)
             res = _throughput(torch, model, args.batch, steps, warmup, 3)
             res["weights_gb"] = round(model.weight_bytes() / 1e9, 3)

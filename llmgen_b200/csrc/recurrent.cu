@@ -101,7 +101,7 @@ LLMK_EXPORT int llmk_short_conv(float* out, long long out_ld, const void* x, lon
                                 int dtype, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0 || C <= 0) return LLMK_OK;
     if (K < 1 || K > MAX_TAPS) LLMK_FAIL("short_conv: %d taps (1 to %d are built)", K, MAX_TAPS);
-    if (!out || !x || !taps || !state || !cu_q || !state_slots) LLMK_FAIL("short_conv: bad arguments");
+    if (!out || !x || !taps || (!state && K > 1) || !cu_q || !state_slots) LLMK_FAIL("short_conv: bad arguments");
     if (act != 0 && act != 1) LLMK_FAIL("short_conv: unknown activation %d (0: none, 1: silu)", act);
     if (n_tokens > 65535 || n_seqs > 65535) LLMK_FAIL("short_conv: a step of %d tokens in %d sequences is too large", n_tokens, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;

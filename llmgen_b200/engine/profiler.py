@@ -290,8 +290,9 @@ def _cost_attention(a, info: PassInfo) -> Tuple[int, int]:
     nq, nkv, hd, window = int(a["nq"]), int(a["nkv"]), int(a["hd"]), int(a["window"] or 0)
     elem = a["kcache"].element_size()
     tokens = sum(info.q_lens)
-    flops = 4 * nq * hd * info.visible_keys(window)
-    bytes_ = 2 * nkv * hd * elem * info.keys_read(window) + 2 * tokens * nq * hd * elem
+    vd = int(a.get("vd") or 0) or hd                       # values of their own width
+    flops = 2 * nq * (hd + vd) * info.visible_keys(window)
+    bytes_ = nkv * (hd + vd) * elem * info.keys_read(window) + tokens * nq * (hd + vd) * elem
     packed = a.get("packed")
     if packed is not None:                                 # the kernel also reads the projection and stores k, v
         bytes_ += _nbytes(packed) + 2 * tokens * int(a.get("nk") or 0) * hd * elem
@@ -320,7 +321,7 @@ def _cost_norm(a, info: PassInfo) -> Tuple[int, int]:
 
 
 def _cost_all_operands(a, info: PassInfo) -> Tuple[int, int]:
-    out = a.get("out", a.get("out_ids"))
+    out = a.get("out", a.get("out_ids", a.get("y", a.get("logits"))))
     flops = out.numel() if hasattr(out, "numel") else 0
     return flops, sum(_nbytes(v) for k, v in a.items() if k != "scratch")
 
@@ -332,6 +333,31 @@ def _cost_linear_attention(a, info: PassInfo) -> Tuple[int, int]:
     flops = tokens * heads * (4 * dim * vdim + min(chunk, max(info.q_lens or (1,))) * (dim + vdim))
     elem = a["packed"].element_size()
     bytes_ = tokens * heads * ((2 * dim + vdim) * elem + vdim * 4) + 2 * seqs * heads * dim * vdim * 4
+    return flops, bytes_
+
+
+def _cost_short_conv(a, info: PassInfo) -> Tuple[int, int]:
+    out, taps = a["out"], a["taps"]
+    n, C = out.shape
+    K = taps.shape[1]
+    return 2 * n * C * K, n * C * (a["x"].element_size() + 4) + _nbytes(taps) + 2 * len(info.q_lens) * (K - 1) * C * 4
+
+
+def _cost_rglru(a, info: PassInfo) -> Tuple[int, int]:
+    u, w = a["u"], a["w_a"]
+    n, C = u.shape
+    blocks = int(a["blocks"])
+    flops = 4 * n * C * (C // blocks) + 12 * n * C          # the two gates' products, the coefficients and the scan
+    # u, y, out, the coefficients written and read again, both matrices, the states
+    bytes_ = n * C * (4 + 2 * a["out"].element_size() + 16) + 2 * _nbytes(w) + 2 * len(info.q_lens) * C * 4
+    return flops, bytes_
+
+
+def _cost_delta_scan(a, info: PassInfo) -> Tuple[int, int]:
+    H, D, E = int(a["heads"]), int(a["dim"]), int(a["vdim"])
+    n = a["out"].shape[0]
+    flops = n * H * (7 * D * E + 12 * D)                   # decay, two dot products and the update over the state, a token
+    bytes_ = _nbytes(a["qkv"]) + _nbytes(a["decay"]) + _nbytes(a["out"]) + 2 * len(info.q_lens) * H * D * E * 4
     return flops, bytes_
 
 
@@ -399,6 +425,8 @@ OP_COSTS: Dict[str, Callable] = {
     "attn_prep": _cost_attn_prep, "gemm_simt": _cost_product, "gemv_bf16": _cost_product, "gemm_tc": _cost_product,
     "gemm_skinny": _cost_product, "gemm_rows8": _cost_product, "gemm_rows8_gated": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,
     "attention_tc": _cost_attention, "sample": _cost_all_operands,
+    "short_conv": _cost_short_conv, "rglru": _cost_rglru, "delta_scan": _cost_delta_scan, "add_bias": _cost_all_operands,
+    "concat_stream": _cost_all_operands, "logit_cap": _cost_all_operands,
 }
 
 

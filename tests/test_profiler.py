@@ -277,7 +277,9 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
     needs = {pf._cost_product: [("w",), ("a", "x"), ("out", "slices")], pf._cost_attention: [("nq",), ("nkv",), ("hd",), ("window",), ("kcache",)],
              pf._cost_attn_prep: [("qkv",), ("nq",), ("nk",), ("hd",), ("rot",), ("kcache",), ("cos",)],
              pf._cost_embed: [("out",), ("table",), ("ids",)], pf._cost_norm: [("out",), ("weight",), ("delta",), ("rows",), ("write_resid",)],
-             pf._cost_all_operands: [("out", "out_ids")], pf._cost_norm_add: [("resid",), ("y",), ("copy",), ("weight",)],
+             pf._cost_all_operands: [("out", "out_ids", "y", "logits")], pf._cost_short_conv: [("out",), ("taps",), ("x",)],
+             pf._cost_rglru: [("u",), ("w_a",), ("blocks",), ("out",)], pf._cost_delta_scan: [("heads",), ("dim",), ("vdim",), ("qkv",), ("decay",), ("out",)],
+             pf._cost_norm_add: [("resid",), ("y",), ("copy",), ("weight",)],
              pf._cost_linear_attention: [("heads",), ("dim",), ("vdim",), ("packed",)],
              pf._cost_latent_attention: [("heads",), ("rank",), ("rot",), ("cache",)],
              pf._cost_latent_absorb: [("q",), ("qa",), ("wuk",), ("heads",), ("dim",), ("rank",)],
