@@ -312,11 +312,11 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      void* scratch, int vd, float softcap, int sink, const void* gate, long long gate_stride,
                                      int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
+    if (hd <= 0 || hd % 8 != 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be a multiple of 8, at most 512", hd);
     if (vd <= 0) vd = hd;
     if (vd % 8 != 0 || vd > 512) LLMK_FAIL("paged_attention: value width %d must be a multiple of 8, at most 512", vd);
     if (softcap < 0.f) LLMK_FAIL("paged_attention: softcap %g", (double)softcap);
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
-    if (hd <= 0 || hd % 8 != 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be a multiple of 8, at most 512", hd);
     if (page_size <= 0) LLMK_FAIL("paged_attention: page_size %d", page_size);
     if (num_parts < 1 || (num_parts > 1 && !scratch)) LLMK_FAIL("paged_attention: bad split (%d parts, scratch %p)", num_parts, scratch);
     if (num_parts > 65535 || nkv > 65535) LLMK_FAIL("paged_attention: grid too large");

@@ -239,6 +239,101 @@ __global__ void rglru_scan_kernel(T* __restrict__ out, long long out_ld, const f
     if (slot >= 0) state[(size_t)slot * state_ld + c] = S;
 }
 
+// The same scan for long portions, in three launches that run side by side over segments of SCAN_SEG tokens: every
+// segment from an empty state (its local states stay in `bx`, the product of its decays and its last local state in
+// `seg`), then a thread per (sequence, channel) takes the carried state through the segments' ends, then every segment
+// adds its share of the state it was entered with.  Segments are counted sequence by sequence: segment j of the launch
+// is the k-th of the first sequence s with j < sum of ceil(n_s' / SCAN_SEG) over s' <= s.
+constexpr int SCAN_SEG = 64;
+
+__device__ __forceinline__ bool find_segment(const int* __restrict__ cu_q, int n_seqs, int j, int* t0, int* t1) {
+    for (int s = 0; s < n_seqs; ++s) {
+        const int beg = cu_q[s], n = cu_q[s + 1] - beg;
+        const int segs = (n + SCAN_SEG - 1) / SCAN_SEG;
+        if (j < segs) {
+            *t0 = beg + j * SCAN_SEG;
+            *t1 = min(*t0 + SCAN_SEG, beg + n);
+            return true;
+        }
+        j -= segs;
+    }
+    return false;
+}
+
+__global__ void rglru_segment_local_kernel(const float* __restrict__ a, float* __restrict__ bx, float* __restrict__ seg_p,
+                                           float* __restrict__ seg_f, const int* __restrict__ cu_q, int n_seqs, int C) {
+    const int j = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    int t0, t1;
+    if (c >= C || !find_segment(cu_q, n_seqs, j, &t0, &t1)) return;
+    float S = 0.f, P = 1.f;
+    for (int t = t0; t < t1; ++t) {
+        const float cv = a[(size_t)t * C + c];
+        S = fmaf(-cv, S, S) + bx[(size_t)t * C + c];
+        P = fmaf(-cv, P, P);
+        bx[(size_t)t * C + c] = S;
+    }
+    seg_p[(size_t)j * C + c] = P;
+    seg_f[(size_t)j * C + c] = S;
+}
+
+// seg_f[j] becomes the state segment j is entered with
+__global__ void rglru_segment_carry_kernel(const float* __restrict__ seg_p, float* __restrict__ seg_f, float* __restrict__ state,
+                                           long long state_ld, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                                           int C) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int n = cu_q[s + 1] - cu_q[s];
+    if (n <= 0) return;
+    int j = 0;
+    for (int k = 0; k < s; ++k) j += (cu_q[k + 1] - cu_q[k] + SCAN_SEG - 1) / SCAN_SEG;
+    const int slot = state_slots[s];
+    float carry = slot >= 0 ? state[(size_t)slot * state_ld + c] : 0.f;
+    const int segs = (n + SCAN_SEG - 1) / SCAN_SEG;
+    for (int k = 0; k < segs; ++k, ++j) {
+        const float in = carry;
+        carry = fmaf(seg_p[(size_t)j * C + c], carry, seg_f[(size_t)j * C + c]);
+        seg_f[(size_t)j * C + c] = in;
+    }
+    if (slot >= 0) state[(size_t)slot * state_ld + c] = carry;
+}
+
+template <typename T>
+__global__ void rglru_segment_finish_kernel(T* __restrict__ out, long long out_ld, const float* __restrict__ a,
+                                            const float* __restrict__ local, const float* __restrict__ seg_in,
+                                            const T* __restrict__ y, long long y_ld, const float* __restrict__ y_bias,
+                                            const int* __restrict__ cu_q, int n_seqs, int C) {
+    const int j = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    int t0, t1;
+    if (c >= C || !find_segment(cu_q, n_seqs, j, &t0, &t1)) return;
+    const float in = seg_in[(size_t)j * C + c];
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    float P = 1.f;
+    for (int t = t0; t < t1; ++t) {
+        const float cv = a[(size_t)t * C + c];
+        P = fmaf(-cv, P, P);
+        const float S = fmaf(P, in, local[(size_t)t * C + c]);
+        out[(size_t)t * out_ld + c] = from_float<T>(S * gelu_tanhf_(to_float(y[(size_t)t * y_ld + c]) + yb));
+    }
+}
+
+// Rows of float32 scratch [rows, C] that `llmk_rglru` needs for a step of this shape: the two coefficient arrays and, for
+// the steps whose scan runs in segments, two values a segment.
+static bool rglru_in_segments(int n_tokens, int dtype) { return dtype == LLMK_BF16 && n_tokens >= 8 * SCAN_SEG; }
+LLMK_EXPORT long long llmk_rglru_scratch_rows(int n_tokens, int n_seqs, int dtype) {
+    long long rows = 2LL * n_tokens;
+    if (rglru_in_segments(n_tokens, dtype)) rows += 2LL * (n_tokens / SCAN_SEG + n_seqs);
+    return rows;
+}
+
 template <typename T>
 static int launch_rglru(void* out, long long out_ld, float* a_buf, float* b_buf, const float* u, const void* Wa, const void* Wi,
                         const float* ba, const float* bi, const float* lam, const void* y, long long y_ld, const float* y_bias,
@@ -270,6 +365,23 @@ static int launch_rglru(void* out, long long out_ld, float* a_buf, float* b_buf,
 #undef LAUNCH_GATES
     LLMK_CHECK_LAUNCH_RC("rglru_gates", e);
     const int threads = 128;
+    if (rglru_in_segments(n_tokens, sizeof(T) == 2 ? LLMK_BF16 : LLMK_F32)) {
+        const int max_segs = n_tokens / SCAN_SEG + n_seqs;
+        float* seg_p = b_buf + (size_t)n_tokens * C;
+        float* seg_f = seg_p + (size_t)max_segs * C;
+        if (max_segs > 65535) LLMK_FAIL("rglru: a step of %d tokens is too large", n_tokens);
+        e = llmk_launch(rglru_segment_local_kernel, dim3(ceil_div(C, threads), max_segs), dim3(threads), 0, s, true,
+                        (const float*)a_buf, b_buf, seg_p, seg_f, cu_q, n_seqs, C);
+        LLMK_CHECK_LAUNCH_RC("rglru_segment_local", e);
+        e = llmk_launch(rglru_segment_carry_kernel, dim3(ceil_div(C, threads), n_seqs), dim3(threads), 0, s, true,
+                        (const float*)seg_p, seg_f, state, state_ld, cu_q, state_slots, C);
+        LLMK_CHECK_LAUNCH_RC("rglru_segment_carry", e);
+        e = llmk_launch(rglru_segment_finish_kernel<T>, dim3(ceil_div(C, threads), max_segs), dim3(threads), 0, s, true, (T*)out,
+                        out_ld, (const float*)a_buf, (const float*)b_buf, (const float*)seg_f, (const T*)y, y_ld, y_bias, cu_q,
+                        n_seqs, C);
+        LLMK_CHECK_LAUNCH_RC("rglru_segment_finish", e);
+        return LLMK_OK;
+    }
     e = llmk_launch(rglru_scan_kernel<T>, dim3(ceil_div(C, threads), n_seqs), dim3(threads), 0, s, true, (T*)out, out_ld,
                     (const float*)a_buf, (const float*)b_buf, (const T*)y, y_ld, y_bias, state, state_ld, cu_q, state_slots, C);
     LLMK_CHECK_LAUNCH_RC("rglru_scan", e);
@@ -277,7 +389,9 @@ static int launch_rglru(void* out, long long out_ld, float* a_buf, float* b_buf,
 }
 
 // out[t, c] (storage dtype) = S_t[c] * gelu_tanh(y[t, c] + y_bias[c]);  u float32 [n_tokens, C] is the convolution's output;
-// a_buf, b_buf: float32 scratch [n_tokens, C] each.
+// a_buf: float32 scratch [n_tokens, C]; b_buf: the same, followed by what `llmk_rglru_scratch_rows` adds for the segments.
+// The float32 engine always scans a sequence's tokens in turn (a thread per channel); the bfloat16 engine cuts steps of
+// 512 tokens and more into segments.
 LLMK_EXPORT int llmk_rglru(void* out, long long out_ld, float* a_buf, float* b_buf, const float* u, const void* Wa, const void* Wi,
                            const float* ba, const float* bi, const float* lam, const void* y, long long y_ld, const float* y_bias,
                            float* state, long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int C,
@@ -393,21 +507,23 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
             const float* kr = ks + tt * DP + slice;
             const float* qr = qs + tt * DP + slice;
             const float* gr = gs + tt * DP + slice;
-            float kS = 0.f;
+            float ks4[4] = {0.f, 0.f, 0.f, 0.f};      // four sums in turn: the chain of dependent adds is a quarter as long
 #pragma unroll
             for (int i = 0; i < DSL; ++i) {
                 S[i] = fmaf(-gr[4 * i], S[i], S[i]);
-                kS = fmaf(kr[4 * i], S[i], kS);
+                ks4[i & 3] = fmaf(kr[4 * i], S[i], ks4[i & 3]);
             }
+            float kS = (ks4[0] + ks4[1]) + (ks4[2] + ks4[3]);
             kS += __shfl_xor_sync(0xffffffffu, kS, 1);
             kS += __shfl_xor_sync(0xffffffffu, kS, 2);
             const float dlt = betas[tt] * (vs[tt * DELTA_COLS + col] - kS);
-            float o = 0.f;
+            float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < DSL; ++i) {
                 S[i] = fmaf(kr[4 * i], dlt, S[i]);
-                o = fmaf(qr[4 * i], S[i], o);
+                o4[i & 3] = fmaf(qr[4 * i], S[i], o4[i & 3]);
             }
+            float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             if (slice == 0 && e < E) p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = o;

@@ -790,6 +790,13 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, taps: torch.Tensor, state: to
            2 if update_state and K > 1 else 1)
 
 
+def rglru_scratch_rows(n_tokens: int, n_seqs: int, dtype: torch.dtype) -> int:
+    """Rows of the float32 scratch [rows, C] that `rglru` needs for a step of this shape."""
+    lib = build.load("recurrent")
+    lib.llmk_rglru_scratch_rows.restype = c_longlong
+    return int(lib.llmk_rglru_scratch_rows(c_int(n_tokens), c_int(n_seqs), c_int(dtype_code(dtype))))
+
+
 def rglru(out: torch.Tensor, scratch: torch.Tensor, u: torch.Tensor, w_a: torch.Tensor, w_i: torch.Tensor,
           b_a: Optional[torch.Tensor], b_i: Optional[torch.Tensor], lam: torch.Tensor, y: torch.Tensor,
           y_bias: Optional[torch.Tensor], state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
@@ -797,11 +804,13 @@ def rglru(out: torch.Tensor, scratch: torch.Tensor, u: torch.Tensor, w_a: torch.
     """The real-gated linear recurrent unit over each sequence's new tokens (csrc/recurrent.cu): gates from u (float32
     [n, C], the convolution's output) by the block-diagonal matrices w_a, w_i [blocks, C/blocks, C/blocks], then
     S = a S + sqrt(1 - a^2) i u from `state` [slots, >= C] and out[n, C] (storage dtype) = S * gelu_tanh(y + y_bias).
-    `scratch`: float32 [2, n, C]."""
+    `scratch`: contiguous float32, `rglru_scratch_rows` rows of C (long steps of the bfloat16 engine scan in segments)."""
     lib = build.load("recurrent")
     n, C = u.shape
-    if u.dtype != torch.float32 or not u.is_contiguous() or scratch.dtype != torch.float32 or scratch.numel() < 2 * n * C:
-        raise KernelError("rglru: u and the scratch [2, n, C] are contiguous float32")
+    need = rglru_scratch_rows(n, n_seqs, out.dtype) * C
+    if u.dtype != torch.float32 or not u.is_contiguous() or scratch.dtype != torch.float32 or scratch.numel() < need \
+            or not scratch.is_contiguous():
+        raise KernelError(f"rglru: u and the scratch ({need} values) are contiguous float32")
     if w_a.dtype != out.dtype or w_i.dtype != out.dtype or y.dtype != out.dtype or not w_a.is_contiguous() or not w_i.is_contiguous():
         raise KernelError("rglru: gate matrices, y and out share the storage dtype")
     if tuple(w_a.shape) != (blocks, C // blocks, C // blocks) or w_i.shape != w_a.shape or state.shape[1] < C:
@@ -811,7 +820,7 @@ def rglru(out: torch.Tensor, scratch: torch.Tensor, u: torch.Tensor, w_a: torch.
                                _ptr(w_a), _ptr(w_i), _ptr(b_a), _ptr(b_i), _ptr(lam), _ptr(y), c_longlong(_row_stride(y)),
                                _ptr(y_bias), _ptr(state), c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots),
                                c_int(n_seqs), c_int(n), c_int(C), c_int(blocks), c_float(decay_scale),
-                               c_int(dtype_code(out.dtype)), _stream()), 2)
+                               c_int(dtype_code(out.dtype)), _stream()), 4 if need > 2 * n * C else 2)
 
 
 def delta_scan(out: torch.Tensor, qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,

@@ -177,9 +177,7 @@ class GQAAttention(Mixer):
 
     def _split(self, ctx):
         """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""
-        if not ctx.pure_decode or self.is_varied:
-            # (a layer with a bound, a sink or a gate: one part, so that a token's logits do not depend on whether
-            # it was decoded alone or beside a portion)
+        if not ctx.pure_decode:
             return 1, 0
         G = self.nq // self.nkv
         chunks = (G + 15) // 16
@@ -277,9 +275,14 @@ class GQAAttention(Mixer):
         o = ws.buffer("attn_o", T, self.nq * self.vd, self.dtype)
         tile_seq = ctx.array(self.tiles_name + "_seq")
         tile_q0 = ctx.array(self.tiles_name + "_q0")
+        # single decoded tokens: the keys in parts that are merged afterwards (the sink enters once, in the merge)
+        parts, part_size = self._split(ctx)
+        scratch = None
+        if parts > 1:
+            scratch = ws.flat("attn_split", ops.attention_scratch_floats(T, self.nq, self.vd, parts), torch.float32)
         ops.paged_attention(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
-                            self.hd, cache.page_size, self.window, float(self.spec.scale), 1, 0, None,
+                            self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch,
                             vd=self.vd, softcap=self.softcap, sink=self.sink, gate=gate)
         out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         if self.o_bias is not None:

@@ -75,7 +75,9 @@ class RGLRU(Mixer):
         ops.short_conv(u, packed[:, C:], self.conv_w, cache.state[:, C:], ctx.cu_q, ctx.state_slots, ctx.n_seqs,
                        in_bias=self.x_b, conv_bias=self.conv_b)
         out = ws.buffer("rglru_out", T, C, self.dtype)
-        scratch = ws.buffer("rglru_coeffs", 2 * T, C, torch.float32, capacity_rows=2 * ws.default_rows)
+        rows = ops.rglru_scratch_rows(T, ctx.n_seqs, self.dtype)
+        scratch = ws.buffer("rglru_coeffs", rows, C, torch.float32,
+                            capacity_rows=ops.rglru_scratch_rows(ws.default_rows, max(ctx.max_seqs_bound, ctx.n_seqs), self.dtype))
         ops.rglru(out, scratch, u, self.w_a, self.w_i, self.b_a, self.b_i, self.lam, packed[:, :C], self.y_b, cache.state,
                   ctx.cu_q, ctx.state_slots, ctx.n_seqs, self.spec.blocks, float(self.spec.decay_scale))
         return linear_sliced(ws, "mixer_out", out, self.w_o, self.dtype)

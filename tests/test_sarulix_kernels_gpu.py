@@ -65,11 +65,12 @@ def test_short_conv_reads_the_last_inputs_of_the_step_before(taps, act, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("lens_first,lens_second", [([37, 1, 64], [1, 30, 3]), ([300, 1, 530], [257, 3, 350])])
 @pytest.mark.parametrize("C,blocks", [(48, 3), (36, 1), (160, 2), (20, 4)])
-def test_rglru_kernels_carry_their_state_between_calls(C, blocks, dtype):
+def test_rglru_kernels_carry_their_state_between_calls(C, blocks, dtype, lens_first, lens_second):
+    """Three sequences, two steps each; the long steps of the bfloat16 engine scan in segments that run side by side."""
     from llmgen_b200.kernels import ops
     n = C // blocks
-    lens_first, lens_second = [37, 1, 64], [1, 30, 3]
     wa, wi = rnd((blocks, n, n), 1, 0.3, DT[dtype]), rnd((blocks, n, n), 2, 0.3, DT[dtype])
     ba, bi, lam, yb = rnd((C,), 3, 0.5), rnd((C,), 4, 0.5), rnd((C,), 5, 2.0) - 3.0, rnd((C,), 6, 0.3)
     us = [rnd((a + b, C), 10 + i) for i, (a, b) in enumerate(zip(lens_first, lens_second))]
@@ -83,8 +84,10 @@ def test_rglru_kernels_carry_their_state_between_calls(C, blocks, dtype):
         y = torch.cat([x[a:b] for x, (a, b) in zip(ys, cut)]).to(DEV)
         T = u.shape[0]
         out = torch.full((T, C), float("nan"), device=DEV, dtype=DT[dtype])
-        ops.rglru(out, torch.empty(2 * T, C, device=DEV), u, wa.to(DEV), wi.to(DEV), ba.to(DEV), bi.to(DEV), lam.to(DEV), y[:, :C],
-                  yb.to(DEV), state, cu, sl, 4, blocks, 8.0)
+        rows = ops.rglru_scratch_rows(T, 4, DT[dtype])
+        assert (rows > 2 * T) == (dtype == "bfloat16" and T >= 512)
+        ops.rglru(out, torch.full((rows, C), float("nan"), device=DEV), u, wa.to(DEV), wi.to(DEV), ba.to(DEV), bi.to(DEV), lam.to(DEV),
+                  y[:, :C], yb.to(DEV), state, cu, sl, 4, blocks, 8.0)
         at = 0
         for i, m in enumerate(lens):
             outs[i].append(out[at:at + m].float().cpu())
@@ -110,13 +113,15 @@ def test_rglru_keeps_a_decay_just_below_one_over_thousands_of_tokens():
     lam = torch.full((C,), -9.0) + rnd((C,), 1, 0.5)
     u, y = rnd((T, C), 2) + 1.0, torch.ones(T, C) * 3.0
     state = torch.zeros(1, C, device=DEV)
-    out = torch.empty(T, C, device=DEV)
     cu, sl = torch.tensor([0, T], dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.rglru(out, torch.empty(2 * T, C, device=DEV), u.to(DEV), wa.to(DEV), wi.to(DEV), None, None, lam.to(DEV), y.to(DEV), None, state,
-              cu, sl, 1, 1, 8.0)
     half = torch.full((T, C), 0.5, dtype=torch.float64)
     S = plain.rglru_scan(u.double(), half, half, lam.double())
-    close(state[0], S[-1], 3e-6)
+    for dt in (torch.float32, torch.bfloat16):                 # a thread per channel; segments side by side
+        state.zero_()
+        out = torch.empty(T, C, device=DEV, dtype=dt)
+        ops.rglru(out, torch.empty(ops.rglru_scratch_rows(T, 1, dt), C, device=DEV), u.to(DEV), wa.to(DEV, dt), wi.to(DEV, dt), None, None,
+                  lam.to(DEV), y.to(DEV, dt), None, state, cu, sl, 1, 1, 8.0)
+        close(state[0], S[-1], 3e-6)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
