@@ -1,0 +1,293 @@
+// Causal grouped-query attention over the paged cache for prompts and prompt portions in bfloat16 whose softmax
+// weights must stay 32-bit: the products run on the tensor cores (`mma.sync.m16n8k16`, bfloat16 operands, float32
+// accumulators), everything between them on the CUDA cores in float32.
+//
+//   S = Q K^T      Q and K are the cache's bfloat16 values, every product exact, sums float32
+//   scores         s * scale, then (softcap > 0) softcap * tanh(s / softcap), the causal (and window) mask, the row's
+//                  running maximum and sum, the weights exp(s - m): float32, `tanhf` and `exp2f` at full precision
+//   O += P V       a float32 weight enters as THREE bfloat16 terms p = p1 + p2 + p3 (24 bits of mantissa), so every
+//                  product with a bfloat16 value is what float32 arithmetic would give; three MMAs a step
+//   finish         the sink (one more term exp(0) in the denominator), the division, the output gate sigmoid(g)
+//
+// Block = 64 queries of one sequence x one query head, four warps of 16 rows; keys in tiles of 64 through shared
+// memory (16-byte copies out of the pages).  Semantics as in csrc/attention.cu (which takes float32, single tokens in
+// parts, and every size this kernel refuses): query j of a portion sits at position ctx - q_len + j.
+// Taken: key width and value width 64 or 128 each.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int BM = 64, BN = 64, WARPS = 4;
+
+struct Params {
+    const bf16* q;
+    const bf16* kcache;
+    const bf16* vcache;
+    bf16* out;
+    const bf16* gate;
+    const int* block_tables;
+    const int* ctx_len;
+    const int* cu_q;
+    const int* tile_seq;
+    const int* tile_q0;
+    long long q_stride, o_stride, gate_stride;
+    int max_blocks, nq, nkv, page_size, window, sink;
+    float scale, softcap;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+// x = a + b + c with a, b, c bfloat16: the three most significant pieces of a float32
+__device__ __forceinline__ void split3(float x, float& a, float& b, float& c) {
+    a = __bfloat162float(__float2bfloat16_rn(x));
+    const float r = x - a;
+    b = __bfloat162float(__float2bfloat16_rn(r));
+    c = __bfloat162float(__float2bfloat16_rn(r - b));
+}
+
+template <int HD, int VD>
+__global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
+    constexpr int QLD = HD + 8, VLD = VD + 8;      // rows 16 bytes longer: the eight rows of an ldmatrix fall on different banks
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][QLD]
+    bf16* Ks = Qs + BM * QLD;                           // [BN][QLD]
+    bf16* Vs = Ks + BN * QLD;                           // [BN][VLD]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int s = p.tile_seq[blockIdx.x];
+    pdl_launch_dependents();
+    pdl_wait();
+    if (s < 0) return;
+    const int q0 = p.tile_q0[blockIdx.x];
+    const int head = blockIdx.y;
+    const int kvh = head / (p.nq / p.nkv);
+    const int q_beg = p.cu_q[s], q_len = p.cu_q[s + 1] - q_beg, ctx = p.ctx_len[s];
+    const int nq_tile = min(BM, q_len - q0);
+    if (nq_tile <= 0 || ctx < q_len) {
+        // rows of padding: zeros
+        for (int idx = threadIdx.x; idx < max(nq_tile, 0) * VD; idx += blockDim.x)
+            p.out[(size_t)(q_beg + q0 + idx / VD) * p.o_stride + (size_t)head * VD + idx % VD] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int first_pos = ctx - q_len + q0;
+    const int k_end = first_pos + nq_tile;
+    const int k_beg = p.window > 0 ? max(0, first_pos - p.window + 1) / BN * BN : 0;
+    const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+
+    for (int idx = threadIdx.x; idx < BM * (HD / 8); idx += blockDim.x) {
+        const int r = idx / (HD / 8), v = idx % (HD / 8);
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r < nq_tile) val = *reinterpret_cast<const uint4*>(p.q + (size_t)(q_beg + q0 + r) * p.q_stride + (size_t)head * HD + v * 8);
+        *reinterpret_cast<uint4*>(Qs + r * QLD + v * 8) = val;
+    }
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int j = 0; j < HD / 16; ++j)
+        ldmatrix_x4(qf[j], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QLD + j * 16 + (lane >> 4) * 8);
+
+    float o[VD / 8][4];
+#pragma unroll
+    for (int n = 0; n < VD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+    const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    for (int t0 = k_beg; t0 < k_end; t0 += BN) {
+        __syncthreads();          // the tile before is consumed
+        for (int idx = threadIdx.x; idx < BN * (HD / 8 + VD / 8); idx += blockDim.x) {
+            const int key = idx / (HD / 8 + VD / 8), v = idx % (HD / 8 + VD / 8);
+            const int kpos = t0 + key;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (kpos < k_end) {
+                const int page = bt[kpos / p.page_size];
+                const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
+                val = v < HD / 8 ? *reinterpret_cast<const uint4*>(p.kcache + row * HD + v * 8)
+                                 : *reinterpret_cast<const uint4*>(p.vcache + row * VD + (v - HD / 8) * 8);
+            }
+            if (v < HD / 8) *reinterpret_cast<uint4*>(Ks + key * QLD + v * 8) = val;
+            else *reinterpret_cast<uint4*>(Vs + key * VLD + (v - HD / 8) * 8) = val;
+        }
+        __syncthreads();
+        // a warp whose rows all lie before this tile's first key has nothing to do in it (causal)
+        if (first_pos + warp * 16 + 15 < t0) continue;
+
+        float sc[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+            for (int n2 = 0; n2 < BN / 16; ++n2) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, Ks + (n2 * 16 + (lane >> 4) * 8 + (lane & 7)) * QLD + j * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(sc[2 * n2], qf[j], kb[0], kb[1]);
+                mma_bf16(sc[2 * n2 + 1], qf[j], kb[2], kb[3]);
+            }
+        }
+        // scores, mask, the rows' maxima
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int kpos = t0 + n * 8 + 2 * tq + (e & 1);
+                float v = sc[n][e] * p.scale;
+                if (p.softcap > 0.f) v = p.softcap * tanhf(v * inv_cap);
+                const bool vis = kpos <= qpos[r] && kpos < k_end && (p.window <= 0 || kpos > qpos[r] - p.window);
+                v = vis ? v : -INFINITY;
+                sc[n][e] = v;
+                mx[r] = fmaxf(mx[r], v);
+            }
+        }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m[r], mx[r]);
+            alpha[r] = (m[r] == -INFINITY) ? 0.f : exp2f((m[r] - m_new) * LOG2E);
+            m[r] = m_new;
+            l[r] *= alpha[r];
+        }
+#pragma unroll
+        for (int n = 0; n < VD / 8; ++n) {
+            o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const float pv = (sc[n][e] == -INFINITY) ? 0.f : exp2f((sc[n][e] - m[r]) * LOG2E);
+                sc[n][e] = pv;
+                l[r] += pv;
+            }
+        }
+        // O += P V, sixteen keys a step, the weights in three bfloat16 terms
+#pragma unroll
+        for (int j = 0; j < BN / 16; ++j) {
+            uint32_t pa[3][4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int n = 2 * j + (q4 >> 1), e = (q4 & 1) * 2;
+                float a0, b0, c0, a1, b1, c1;
+                split3(sc[n][e], a0, b0, c0);
+                split3(sc[n][e + 1], a1, b1, c1);
+                pa[0][q4] = pack2(a0, a1);
+                pa[1][q4] = pack2(b0, b1);
+                pa[2][q4] = pack2(c0, c1);
+            }
+#pragma unroll
+            for (int n2 = 0; n2 < VD / 16; ++n2) {
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, Vs + (j * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + n2 * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int term = 2; term >= 0; --term) {          // smallest terms first
+                    mma_bf16(o[2 * n2], pa[term], vb[0], vb[1]);
+                    mma_bf16(o[2 * n2 + 1], pa[term], vb[2], vb[3]);
+                }
+            }
+        }
+    }
+    // the rows' sums over the four threads that share a row, the sink, the gate, the division
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + g + r * 8;
+        if (row >= nq_tile) continue;
+        float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+        if (p.sink && l[r] > 0.f) {
+            const float M = fmaxf(m[r], 0.f);
+            const float w = expf(m[r] - M);
+            inv = w / (l[r] * w + expf(-M));
+        }
+        const size_t tok = (size_t)(q_beg + q0 + row);
+        bf16* dst = p.out + tok * p.o_stride + (size_t)head * VD;
+        const bf16* gt = p.gate ? p.gate + tok * p.gate_stride + (size_t)head * VD : nullptr;
+#pragma unroll
+        for (int n = 0; n < VD / 8; ++n) {
+            const int col = n * 8 + 2 * tq;
+            float v0 = o[n][2 * r] * inv, v1 = o[n][2 * r + 1] * inv;
+            if (gt) {
+                v0 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
+                v1 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col + 1])));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(v0, v1);
+        }
+    }
+}
+
+template <int HD, int VD>
+int launch(const Params& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = ((size_t)(BM + BN) * (HD + 8) + (size_t)BN * (VD + 8)) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LLMK_FAIL("attention_mma: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    LLMK_CHECK_LAUNCH_RC("attention_mma", llmk_launch(attention_mma_kernel<HD, VD>, grid, dim3(WARPS * 32), smem, s, true, p));
+    return LLMK_OK;
+}
+
+}  // namespace
+
+// Queries per tile (0: the kernel does not take these sizes).
+LLMK_EXPORT int llmk_attention_mma_tile_queries(int nq, int nkv, int hd, int vd) {
+    if (nkv <= 0 || nq <= 0 || nq % nkv != 0) return 0;
+    if ((hd != 64 && hd != 128) || (vd != 64 && vd != 128)) return 0;
+    return BM;
+}
+
+// out[t, nq*vd] (bfloat16) = attention of q[t] (bfloat16) over the paged cache [pages, nkv, page_size, hd | vd].
+// tile_seq / tile_q0 list tiles of 64 queries; an entry with sequence -1 is skipped.
+LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q, long long q_stride, const void* kcache,
+                                   const void* vcache, const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
+                                   const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd, int vd,
+                                   int page_size, int window, float scale, float softcap, int sink, const void* gate,
+                                   long long gate_stride, void* stream) {
+    if (n_tiles <= 0) return LLMK_OK;
+    if (llmk_attention_mma_tile_queries(nq, nkv, hd, vd) == 0)
+        LLMK_FAIL("attention_mma: not taken (heads %d/%d, key width %d and value width %d must be 64 or 128)", nq, nkv, hd, vd);
+    if (q_stride % 8 != 0 || o_stride % 2 != 0 || !host_aligned16(q) || !host_aligned16(kcache) || !host_aligned16(vcache) ||
+        (reinterpret_cast<uintptr_t>(out) & 3) != 0 || page_size <= 0)
+        LLMK_FAIL("attention_mma: q and the cache must start on 16-byte boundaries, q's row stride a multiple of 8");
+    if (nq > 65535) LLMK_FAIL("attention_mma: grid too large");
+    Params p;
+    p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
+    p.gate = (const bf16*)gate; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.q_stride = q_stride; p.o_stride = o_stride; p.gate_stride = gate_stride;
+    p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.sink = sink ? 1 : 0;
+    p.scale = scale; p.softcap = softcap;
+    dim3 grid(n_tiles, nq);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64 && vd == 64) return launch<64, 64>(p, grid, s);
+    if (hd == 64) return launch<64, 128>(p, grid, s);
+    if (vd == 64) return launch<128, 64>(p, grid, s);
+    return launch<128, 128>(p, grid, s);
+}

@@ -268,14 +268,17 @@ __global__ void rglru_segment_local_kernel(const float* __restrict__ a, float* _
     pdl_wait();
     int t0, t1;
     if (c >= C || !find_segment(cu_q, n_seqs, j, &t0, &t1)) return;
-    float S = 0.f, P = 1.f;
+    // the product of the segment's decays as the exponential of their logarithms' sum: a running product would be
+    // rounded at every token, always the same way where the decays hardly change, and the carried state takes a
+    // segment's error 1 / (1 - product) times
+    float S = 0.f, L = 0.f;
     for (int t = t0; t < t1; ++t) {
         const float cv = a[(size_t)t * C + c];
         S = fmaf(-cv, S, S) + bx[(size_t)t * C + c];
-        P = fmaf(-cv, P, P);
+        L += log1pf(-cv);
         bx[(size_t)t * C + c] = S;
     }
-    seg_p[(size_t)j * C + c] = P;
+    seg_p[(size_t)j * C + c] = expf(L);
     seg_f[(size_t)j * C + c] = S;
 }
 
@@ -316,11 +319,10 @@ __global__ void rglru_segment_finish_kernel(T* __restrict__ out, long long out_l
     if (c >= C || !find_segment(cu_q, n_seqs, j, &t0, &t1)) return;
     const float in = seg_in[(size_t)j * C + c];
     const float yb = y_bias ? y_bias[c] : 0.f;
-    float P = 1.f;
+    float L = 0.f;
     for (int t = t0; t < t1; ++t) {
-        const float cv = a[(size_t)t * C + c];
-        P = fmaf(-cv, P, P);
-        const float S = fmaf(P, in, local[(size_t)t * C + c]);
+        L += log1pf(-a[(size_t)t * C + c]);
+        const float S = fmaf(expf(L), in, local[(size_t)t * C + c]);
         out[(size_t)t * out_ld + c] = from_float<T>(S * gelu_tanhf_(to_float(y[(size_t)t * y_ld + c]) + yb));
     }
 }
@@ -411,45 +413,136 @@ LLMK_EXPORT int llmk_rglru(void* out, long long out_ld, float* a_buf, float* b_b
 }
 
 // ------------------------------------------------------------------------------------------------ gated delta rule
-// Block (sequence, head, tile of 64 value columns), 256 threads: a lane holds a quarter of one column of S (key channels
-// slice, slice + 4, ...), so the two dot products of a token over the key channels end in two shuffles.  The tokens of
-// a portion come in chunks of DELTA_CHUNK: all threads first prepare the chunk in shared memory (q and k made unit
-// vectors, q scaled, the decays exponentiated, beta through its sigmoid), then the columns walk the chunk token by token.
+// Two launches.  `delta_prep`, a block per token, works in place: q and k (float32, after convolution and silu) become
+// unit vectors per head (q also times key_dim^-1/2), the decays' pre-activations become 1 - g = -expm1(-exp(A_log_h)
+// softplus(x + dt_bias)) (a decay just below 1 keeps its digits only as its distance from 1), beta goes through its sigmoid,
+// and q . k of every key head is left beside it.  With S' = diag(g) S the token's read-out is
+// o = S^T q = S'^T q + (q . k) d, so both dot products over the key channels run over S' in one pass and the update
+// S = S' + k d^T ends the token: one chain of dependent steps a token instead of two.
+// `delta_scan`, a block per (sequence, head, tile of DELTA_COLS value columns) of 4 * DELTA_COLS threads: a lane holds a
+// quarter of one column of S (a contiguous run of key channels), so the two dot products of a token over the key
+// channels end in two shuffles.  The tokens come in chunks of DELTA_CHUNK through shared memory, the next chunk copied
+// (cp.async) while the columns walk the present one token by token.
 constexpr int DELTA_CHUNK = 16;
-constexpr int DELTA_COLS = 64;
+constexpr int DELTA_COLS = 32;
+constexpr int DELTA_THREADS = 4 * DELTA_COLS;
+
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prep_kernel(float* __restrict__ qkv, long long qkv_ld, float* __restrict__ decay,
+                                                         float* __restrict__ beta_out, const T* __restrict__ beta, long long beta_ld,
+                                                         const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                                         int H, int G, int D, float unit_eps, float q_scale) {
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int head = warp; head < G; head += warps) {              // q and k of one key head, and their dot product
+        float* xq = qkv + t * qkv_ld + (size_t)head * D;
+        float* xk = xq + (size_t)G * D;
+        float sq = 0.f, sk = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            sq += xq[d] * xq[d];
+            sk += xk[d] * xk[d];
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.0f / sqrtf(sk + unit_eps);
+        float dot = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float qv = xq[d] * fq, kv = xk[d] * fk;
+            xq[d] = qv;
+            xk[d] = kv;
+            dot = fmaf(qv, kv, dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) beta_out[t * (H + G) + H + head] = dot;
+    }
+    const int HD = H * D;
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+        const float neg_exp_a = -expf(a_log[i / D]);
+        decay[t * HD + i] = -expm1f(neg_exp_a * softplusf_(decay[t * HD + i] + dt_bias[i]));
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) beta_out[t * (H + G) + h] = sigmoidf_(to_float(beta[t * beta_ld + h]));
+}
 
 struct DeltaParams {
     float* out;              // [n_tokens, H * E]
-    const float* qkv;        // [n_tokens, ld]: q at column 0, k at G * D, v at 2 * G * D (after convolution and silu)
+    const float* qkv;        // [n_tokens, ld]: q at column 0, k at G * D, v at 2 * G * D, prepared
     long long qkv_ld;
-    const void* beta;        // [n_tokens, ldb] storage dtype, column h
-    long long beta_ld;
-    const float* decay;      // [n_tokens, H * D] float32, before dt_bias and softplus
-    const float* dt_bias;    // [H * D]
-    const float* a_log;      // [H]
+    const float* beta;       // [n_tokens, H + G]: beta of every head, then q . k of every key head
+    const float* decay;      // [n_tokens, H * D]: 1 - g
     float* state;            // [slots, state_ld]: S [H][D][E]
     long long state_ld;
     const int* cu_q;
     const int* state_slots;
-    int H, G, D, E;
-    float unit_eps, q_scale;
+    int H, G, D, E, vec_ok;
 };
 
-template <typename T, int DSL>
-__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
-    constexpr int DP = 4 * DSL;
-    extern __shared__ float sm[];
-    float* qs = sm;                                  // [CHUNK][DP]
-    float* ks = qs + DELTA_CHUNK * DP;
-    float* gs = ks + DELTA_CHUNK * DP;
-    float* vs = gs + DELTA_CHUNK * DP;               // [CHUNK][COLS]
-    float* betas = vs + DELTA_CHUNK * DELTA_COLS;    // [CHUNK]
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// One chunk's rows into shared memory: q, k, 1 - g as [CHUNK][4 slices][DSL + 4] (the padding keeps the four slices'
+// 16-byte reads on different banks), v as [CHUNK][COLS], beta [CHUNK].
+template <int DSL>
+__device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* buf, int t_first, int nc, int h, int kvh, int e0) {
+    constexpr int ROW = 4 * (DSL + 4);
+    float* qs = buf;
+    float* ks = qs + DELTA_CHUNK * ROW;
+    float* gs = ks + DELTA_CHUNK * ROW;
+    float* vs = gs + DELTA_CHUNK * ROW;
+    float* bs = vs + DELTA_CHUNK * DELTA_COLS;
+    const int D = p.D, E = p.E, GD = p.G * p.D;
+    if (p.vec_ok) {
+        const int vecs = D / 4;
+        for (int idx = threadIdx.x; idx < nc * vecs; idx += DELTA_THREADS) {
+            const int tt = idx / vecs, d = (idx % vecs) * 4;
+            const size_t t = (size_t)(t_first + tt);
+            const int at = tt * ROW + (d / DSL) * (DSL + 4) + d % DSL;
+            cp_async16(qs + at, p.qkv + t * p.qkv_ld + (size_t)kvh * D + d);
+            cp_async16(ks + at, p.qkv + t * p.qkv_ld + GD + (size_t)kvh * D + d);
+            cp_async16(gs + at, p.decay + t * ((size_t)p.H * D) + (size_t)h * D + d);
+        }
+        for (int idx = threadIdx.x; idx < nc * (DELTA_COLS / 4); idx += DELTA_THREADS) {
+            const int tt = idx / (DELTA_COLS / 4), cc = (idx % (DELTA_COLS / 4)) * 4;
+            if (e0 + cc < E) cp_async16(vs + tt * DELTA_COLS + cc, p.qkv + (size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < nc * D; idx += DELTA_THREADS) {
+            const int tt = idx / D, d = idx % D;
+            const size_t t = (size_t)(t_first + tt);
+            const int at = tt * ROW + (d / DSL) * (DSL + 4) + d % DSL;
+            qs[at] = p.qkv[t * p.qkv_ld + (size_t)kvh * D + d];
+            ks[at] = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
+            gs[at] = p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d];
+        }
+        for (int idx = threadIdx.x; idx < nc * DELTA_COLS; idx += DELTA_THREADS) {
+            const int tt = idx / DELTA_COLS, cc = idx % DELTA_COLS;
+            if (e0 + cc < E) vs[idx] = p.qkv[(size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc];
+        }
+    }
+    if (threadIdx.x < nc) {
+        const float* row = p.beta + (size_t)(t_first + threadIdx.x) * (p.H + p.G);
+        bs[threadIdx.x] = row[h];
+        bs[DELTA_CHUNK + threadIdx.x] = row[p.H + kvh];
+    }
+}
+
+template <int DSL>
+__global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p) {
+    constexpr int ROW = 4 * (DSL + 4);
+    constexpr int BUF = DELTA_CHUNK * (3 * ROW + DELTA_COLS) + 2 * DELTA_CHUNK;
+    extern __shared__ __align__(16) float sm[];
     const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * DELTA_COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slice = lane & 3, col = warp * 8 + (lane >> 2);
     const int e = e0 + col;
     const int D = p.D, E = p.E;
     const int kvh = h / (p.H / p.G);
+    // channels beyond key_dim, and value columns beyond value_dim, hold zeros throughout (no decay: 1 - g = 0)
+    for (int i = threadIdx.x; i < 2 * BUF; i += DELTA_THREADS) sm[i] = 0.f;
     pdl_launch_dependents();
     pdl_wait();
     const int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
@@ -459,123 +552,113 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p) {
     float* st = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
 #pragma unroll
     for (int i = 0; i < DSL; ++i) {
-        const int d = slice + 4 * i;
+        const int d = slice * DSL + i;
         S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
     }
-    const float neg_exp_a = -expf(p.a_log[h]);
-    const int GD = p.G * D;
-    const T* beta = static_cast<const T*>(p.beta);
-    for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK) {
+    __syncthreads();
+    delta_load_chunk<DSL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, kvh, e0);
+    int turn = 0;
+    for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK, turn ^= 1) {
         const int nc = min(DELTA_CHUNK, n - c0);
-        __syncthreads();      // the chunk before is consumed
-        for (int idx = threadIdx.x; idx < DELTA_CHUNK * DP; idx += 256) {
-            const int tt = idx / DP, d = idx % DP;
-            float qv = 0.f, kv = 0.f, gv = 0.f;      // gv: 1 - g (a decay just below 1 is held exactly enough only so)
-            if (tt < nc && d < D) {
-                const size_t t = (size_t)(q_beg + c0 + tt);
-                qv = p.qkv[t * p.qkv_ld + (size_t)kvh * D + d];
-                kv = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
-                gv = -expm1f(neg_exp_a * softplusf_(p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d] + p.dt_bias[(size_t)h * D + d]));
-            }
-            qs[idx] = qv;
-            ks[idx] = kv;
-            gs[idx] = gv;
-        }
-        for (int idx = threadIdx.x; idx < DELTA_CHUNK * DELTA_COLS; idx += 256) {
-            const int tt = idx / DELTA_COLS, cc = idx % DELTA_COLS;
-            vs[idx] = (tt < nc && e0 + cc < E) ? p.qkv[(size_t)(q_beg + c0 + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc] : 0.f;
-        }
-        if (threadIdx.x < DELTA_CHUNK)
-            betas[threadIdx.x] = threadIdx.x < nc ? sigmoidf_(to_float(beta[(size_t)(q_beg + c0 + threadIdx.x) * p.beta_ld + h])) : 0.f;
-        __syncthreads();
-        for (int tt = warp; tt < nc; tt += 8) {      // unit vectors: a warp per token
-            float sq = 0.f, sk = 0.f;
-            for (int d = lane; d < DP; d += 32) {
-                sq += qs[tt * DP + d] * qs[tt * DP + d];
-                sk += ks[tt * DP + d] * ks[tt * DP + d];
-            }
-            sq = warp_sum(sq);
-            sk = warp_sum(sk);
-            const float fq = p.q_scale / sqrtf(sq + p.unit_eps), fk = 1.0f / sqrtf(sk + p.unit_eps);
-            for (int d = lane; d < DP; d += 32) {
-                qs[tt * DP + d] *= fq;
-                ks[tt * DP + d] *= fk;
-            }
-        }
-        __syncthreads();
+        cp_async_wait_all();
+        __syncthreads();      // this chunk has arrived, and the chunk before is consumed by every warp
+        if (c0 + DELTA_CHUNK < n)
+            delta_load_chunk<DSL>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, kvh, e0);
+        const float* buf = sm + turn * BUF;
+        const float* vs = buf + 3 * DELTA_CHUNK * ROW;
+        const float* bs = vs + DELTA_CHUNK * DELTA_COLS;
         for (int tt = 0; tt < nc; ++tt) {
-            const float* kr = ks + tt * DP + slice;
-            const float* qr = qs + tt * DP + slice;
-            const float* gr = gs + tt * DP + slice;
-            float ks4[4] = {0.f, 0.f, 0.f, 0.f};      // four sums in turn: the chain of dependent adds is a quarter as long
+            const float4* qr = reinterpret_cast<const float4*>(buf + tt * ROW + slice * (DSL + 4));
+            const float4* kr = reinterpret_cast<const float4*>(buf + DELTA_CHUNK * ROW + tt * ROW + slice * (DSL + 4));
+            const float4* gr = reinterpret_cast<const float4*>(buf + 2 * DELTA_CHUNK * ROW + tt * ROW + slice * (DSL + 4));
+            float ks4[4] = {0.f, 0.f, 0.f, 0.f}, qs4[4] = {0.f, 0.f, 0.f, 0.f};   // four sums in turn: short chains of dependent adds
 #pragma unroll
-            for (int i = 0; i < DSL; ++i) {
-                S[i] = fmaf(-gr[4 * i], S[i], S[i]);
-                ks4[i & 3] = fmaf(kr[4 * i], S[i], ks4[i & 3]);
+            for (int i = 0; i < DSL / 4; ++i) {
+                const float4 g4 = gr[i], k4 = kr[i], q4 = qr[i];
+                S[4 * i] = fmaf(-g4.x, S[4 * i], S[4 * i]);
+                S[4 * i + 1] = fmaf(-g4.y, S[4 * i + 1], S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(-g4.z, S[4 * i + 2], S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(-g4.w, S[4 * i + 3], S[4 * i + 3]);
+                ks4[0] = fmaf(k4.x, S[4 * i], ks4[0]);
+                ks4[1] = fmaf(k4.y, S[4 * i + 1], ks4[1]);
+                ks4[2] = fmaf(k4.z, S[4 * i + 2], ks4[2]);
+                ks4[3] = fmaf(k4.w, S[4 * i + 3], ks4[3]);
+                qs4[0] = fmaf(q4.x, S[4 * i], qs4[0]);
+                qs4[1] = fmaf(q4.y, S[4 * i + 1], qs4[1]);
+                qs4[2] = fmaf(q4.z, S[4 * i + 2], qs4[2]);
+                qs4[3] = fmaf(q4.w, S[4 * i + 3], qs4[3]);
             }
             float kS = (ks4[0] + ks4[1]) + (ks4[2] + ks4[3]);
+            float qS = (qs4[0] + qs4[1]) + (qs4[2] + qs4[3]);
             kS += __shfl_xor_sync(0xffffffffu, kS, 1);
+            qS += __shfl_xor_sync(0xffffffffu, qS, 1);
             kS += __shfl_xor_sync(0xffffffffu, kS, 2);
-            const float dlt = betas[tt] * (vs[tt * DELTA_COLS + col] - kS);
-            float o4[4] = {0.f, 0.f, 0.f, 0.f};
+            qS += __shfl_xor_sync(0xffffffffu, qS, 2);
+            const float dlt = bs[tt] * (vs[tt * DELTA_COLS + col] - kS);
+            const float o = fmaf(bs[DELTA_CHUNK + tt], dlt, qS);
 #pragma unroll
-            for (int i = 0; i < DSL; ++i) {
-                S[i] = fmaf(kr[4 * i], dlt, S[i]);
-                o4[i & 3] = fmaf(qr[4 * i], S[i], o4[i & 3]);
+            for (int i = 0; i < DSL / 4; ++i) {
+                const float4 k4 = kr[i];
+                S[4 * i] = fmaf(k4.x, dlt, S[4 * i]);
+                S[4 * i + 1] = fmaf(k4.y, dlt, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(k4.z, dlt, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(k4.w, dlt, S[4 * i + 3]);
             }
-            float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
             if (slice == 0 && e < E) p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = o;
         }
     }
     if (st) {
 #pragma unroll
         for (int i = 0; i < DSL; ++i) {
-            const int d = slice + 4 * i;
+            const int d = slice * DSL + i;
             if (d < D && e < E) st[(size_t)d * E + e] = S[i];
         }
     }
 }
 
-template <typename T, int DSL>
+template <int DSL>
 static cudaError_t launch_delta(const DeltaParams& p, dim3 grid, cudaStream_t s) {
-    const size_t smem = ((size_t)DELTA_CHUNK * (3 * 4 * DSL + DELTA_COLS) + DELTA_CHUNK) * sizeof(float);
+    const size_t smem = 2 * ((size_t)DELTA_CHUNK * (3 * 4 * (DSL + 4) + DELTA_COLS) + 2 * DELTA_CHUNK) * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, DSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return llmk_launch(delta_scan_kernel<T, DSL>, grid, dim3(256), smem, s, true, p);
+    return llmk_launch(delta_scan_kernel<DSL>, grid, dim3(DELTA_THREADS), smem, s, true, p);
 }
 
-template <typename T>
-static cudaError_t dispatch_delta(const DeltaParams& p, dim3 grid, cudaStream_t s) {
-    if (p.D <= 32) return launch_delta<T, 8>(p, grid, s);
-    if (p.D <= 64) return launch_delta<T, 16>(p, grid, s);
-    if (p.D <= 128) return launch_delta<T, 32>(p, grid, s);
-    return launch_delta<T, 64>(p, grid, s);
-}
-
-// dtype: of `beta` (the storage dtype of the projection it is a column of); everything else is float32.
-LLMK_EXPORT int llmk_delta_scan(float* out, const float* qkv, long long qkv_ld, const void* beta, long long beta_ld, const float* decay,
-                                const float* dt_bias, const float* a_log, float* state, long long state_ld, const int* cu_q,
-                                const int* state_slots, int n_seqs, int H, int G, int D, int E, float unit_eps, float q_scale,
-                                int dtype, void* stream) {
-    if (n_seqs <= 0) return LLMK_OK;
+// qkv float32 [n_tokens, >= 2 G D + H E] and decay float32 [n_tokens, H D] are rewritten in place by the preparation;
+// beta_buf: float32 scratch [n_tokens, H + G].  dtype: of `beta` (the storage dtype of the projection it is a column of).
+LLMK_EXPORT int llmk_delta_scan(float* out, float* qkv, long long qkv_ld, const void* beta, long long beta_ld, float* decay,
+                                float* beta_buf, const float* dt_bias, const float* a_log, float* state, long long state_ld,
+                                const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int H, int G, int D, int E,
+                                float unit_eps, float q_scale, int dtype, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return LLMK_OK;
     if (H <= 0 || G <= 0 || H % G != 0) LLMK_FAIL("delta_scan: %d heads are not a multiple of %d key heads", H, G);
     if (D <= 0 || D > 256 || E <= 0) LLMK_FAIL("delta_scan: key width %d (at most 256) or value width %d", D, E);
-    if (!out || !qkv || !beta || !decay || !dt_bias || !a_log || !state || !cu_q || !state_slots) LLMK_FAIL("delta_scan: bad arguments");
+    if (!out || !qkv || !beta || !decay || !beta_buf || !dt_bias || !a_log || !state || !cu_q || !state_slots) LLMK_FAIL("delta_scan: bad arguments");
     if (H > 65535 || ceil_div(E, DELTA_COLS) > 65535) LLMK_FAIL("delta_scan: grid too large");
-    DeltaParams p;
-    p.out = out; p.qkv = qkv; p.qkv_ld = qkv_ld; p.beta = beta; p.beta_ld = beta_ld; p.decay = decay; p.dt_bias = dt_bias;
-    p.a_log = a_log; p.state = state; p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots;
-    p.H = H; p.G = G; p.D = D; p.E = E; p.unit_eps = unit_eps; p.q_scale = q_scale;
-    dim3 grid(n_seqs, H, ceil_div(E, DELTA_COLS));
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (dtype == LLMK_F32) e = dispatch_delta<float>(p, grid, s);
-    else if (dtype == LLMK_BF16) e = dispatch_delta<bf16>(p, grid, s);
-    else LLMK_FAIL("delta_scan: unknown dtype %d", dtype);
+    if (dtype == LLMK_F32)
+        e = llmk_launch(delta_prep_kernel<float>, dim3(n_tokens), dim3(256), 0, s, true, qkv, qkv_ld, decay, beta_buf, (const float*)beta,
+                        beta_ld, dt_bias, a_log, H, G, D, unit_eps, q_scale);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(delta_prep_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, true, qkv, qkv_ld, decay, beta_buf, (const bf16*)beta,
+                        beta_ld, dt_bias, a_log, H, G, D, unit_eps, q_scale);
+    else
+        LLMK_FAIL("delta_scan: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("delta_prep", e);
+    DeltaParams p;
+    p.out = out; p.qkv = qkv; p.qkv_ld = qkv_ld; p.beta = beta_buf; p.decay = decay;
+    p.state = state; p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots;
+    p.H = H; p.G = G; p.D = D; p.E = E;
+    // 16-byte copies: every row of q, k, v and of the decays begins on a 16-byte boundary
+    p.vec_ok = (D % 4 == 0 && E % 4 == 0 && qkv_ld % 4 == 0 && host_aligned16(qkv) && host_aligned16(decay)) ? 1 : 0;
+    dim3 grid(n_seqs, H, ceil_div(E, DELTA_COLS));
+    if (D <= 32) e = launch_delta<8>(p, grid, s);
+    else if (D <= 64) e = launch_delta<16>(p, grid, s);
+    else if (D <= 128) e = launch_delta<32>(p, grid, s);
+    else e = launch_delta<64>(p, grid, s);
     LLMK_CHECK_LAUNCH_RC("delta_scan", e);
     return LLMK_OK;
 }

@@ -48,6 +48,7 @@ MODULES: Dict[str, List[str]] = {
     "attention": [],
     "attention_decode": [],
     "attention_tc": [],
+    "attention_mma": [],
     "sampling": [],
     "rowwise": [],
     "linear_attention": [],

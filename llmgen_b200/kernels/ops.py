@@ -554,6 +554,27 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
            2 if num_parts > 1 else 1)
 
 
+def attention_mma_tile_queries(nq: int, nkv: int, hd: int, vd: int) -> int:
+    """Queries per tile of `attention_mma` (0: it does not take these sizes)."""
+    return int(build.load("attention_mma").llmk_attention_mma_tile_queries(c_int(nq), c_int(nkv), c_int(hd), c_int(vd)))
+
+
+def attention_mma(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                  max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
+                  n_tiles: int, nq: int, nkv: int, hd: int, vd: int, page_size: int, window: int, scale: float,
+                  softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
+    """Prompt portions in bfloat16 with 32-bit softmax weights on the tensor cores (csrc/attention_mma.cu): the same
+    result as `paged_attention` with these options, tiles of `attention_mma_tile_queries` queries."""
+    lib = build.load("attention_mma")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or (gate is not None and gate.dtype != torch.bfloat16):
+        raise KernelError("attention_mma: bfloat16 only")
+    _check(lib, lib.llmk_attention_mma(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(_row_stride(q)), _ptr(kcache),
+                                       _ptr(vcache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq),
+                                       _ptr(tile_q0), c_int(n_tiles), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(page_size),
+                                       c_int(window), c_float(scale), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
+                                       c_longlong(_row_stride(gate) if gate is not None else 0), _stream()))
+
+
 def attention_decode_set_cluster_merge(on: bool) -> None:
     """Whether `attention_decode` merges up to 8 key parts through the shared memory of a thread-block
     cluster (the default) or through global memory and a ticket (for measurements and tests)."""
@@ -825,22 +846,25 @@ def rglru(out: torch.Tensor, scratch: torch.Tensor, u: torch.Tensor, w_a: torch.
 
 def delta_scan(out: torch.Tensor, qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
                a_log: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
-               heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float, q_scale: float) -> None:
+               heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float, q_scale: float, beta_buf: torch.Tensor) -> None:
     """The gated delta rule with a decay per key channel over each sequence's new tokens (csrc/recurrent.cu).  qkv float32
     [n, 2 kv_heads dim + heads vdim] (after convolution and silu); beta [n, heads] (storage dtype, any row stride, before
     its sigmoid); decay float32 [n, heads dim] (before dt_bias and softplus); state [slots, >= heads dim vdim] float32;
-    out float32 [n, heads vdim]."""
+    out float32 [n, heads vdim].  `qkv` and `decay` are REWRITTEN (q and k as unit vectors, 1 - g); `beta_buf`: float32
+    scratch [n, heads + kv_heads]."""
     lib = build.load("recurrent")
     n = out.shape[0]
-    if out.dtype != torch.float32 or qkv.dtype != torch.float32 or decay.dtype != torch.float32 or state.dtype != torch.float32:
-        raise KernelError("delta_scan: out, qkv, decay and state are float32")
+    if out.dtype != torch.float32 or qkv.dtype != torch.float32 or decay.dtype != torch.float32 or state.dtype != torch.float32 \
+            or beta_buf.dtype != torch.float32:
+        raise KernelError("delta_scan: out, qkv, decay, state and the scratch are float32")
     if not out.is_contiguous() or not decay.is_contiguous() or out.shape[1] != heads * vdim or decay.shape[1] != heads * dim \
-            or qkv.shape[1] != 2 * kv_heads * dim + heads * vdim or state.shape[1] < heads * dim * vdim:
+            or qkv.shape[1] != 2 * kv_heads * dim + heads * vdim or state.shape[1] < heads * dim * vdim or beta_buf.numel() < n * (heads + kv_heads) \
+            or not beta_buf.is_contiguous():
         raise KernelError("delta_scan: shapes do not fit")
     _check(lib, lib.llmk_delta_scan(_ptr(out), _ptr(qkv), c_longlong(_row_stride(qkv)), _ptr(beta), c_longlong(_row_stride(beta)),
-                                    _ptr(decay), _ptr(dt_bias), _ptr(a_log), _ptr(state), c_longlong(_row_stride(state)),
-                                    _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(heads), c_int(kv_heads), c_int(dim),
-                                    c_int(vdim), c_float(unit_eps), c_float(q_scale), c_int(dtype_code(beta.dtype)), _stream()))
+                                    _ptr(decay), _ptr(beta_buf), _ptr(dt_bias), _ptr(a_log), _ptr(state), c_longlong(_row_stride(state)),
+                                    _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(heads), c_int(kv_heads), c_int(dim),
+                                    c_int(vdim), c_float(unit_eps), c_float(q_scale), c_int(dtype_code(beta.dtype)), _stream()), 2)
 
 
 # ------------------------------------------------------------------------------ linear attention

@@ -56,8 +56,10 @@ class GQAAttention(Mixer):
     Variations (`AttentionSpec`): biases on the projections, values of another width than keys, a bound on the scores
     (softcap), a sink in the softmax's denominator and an output gate.  The gate's matrix is packed behind q, k and v,
     the biases of q, k and v are added by the preparation kernel before the per-head norms, and bound, sink and gate
-    are applied inside the general attention kernel (csrc/attention.cu), which takes every step of a layer that has
-    any of them; the output projection's bias is added to its result (or to the first of its slices)."""
+    are applied inside the attention kernels that take the steps of a layer that has any of them: in bfloat16 portions of
+    prompts run on the tensor cores with float32 softmax weights (csrc/attention_mma.cu), single decoded tokens (their
+    keys in parts), float32 and other sizes on the general kernel (csrc/attention.cu); the output projection's bias is
+    added to its result (or to the first of its slices)."""
 
     # what `prepare_step` adds depends on the lengths of the step's portions only, not on their
     # positions or requests: the engine may keep it across decode steps of one batch size
@@ -86,7 +88,7 @@ class GQAAttention(Mixer):
     @staticmethod
     def kernel_modules(spec):
         if GQAAttention.varied(spec):
-            return ("attn_prep", "attention", "rowwise") + GEMM_MODULES
+            return ("attn_prep", "attention", "attention_mma", "rowwise") + GEMM_MODULES
         return ("attn_prep", "attention", "attention_decode", "attention_tc") + GEMM_MODULES
 
     @staticmethod
@@ -142,6 +144,7 @@ class GQAAttention(Mixer):
         self.bq = ops.attention_tile_queries(self.nq, self.nkv)
         self.tiles_name = f"attention_tiles_bq{self.bq}"
         self._tc_bq = {}       # page size -> queries per tile of the tensor-core kernel (0: not taken)
+        self._mma_bq = None
 
     # -- what the engine asks
     def cache_request(self) -> KVRequest:
@@ -161,6 +164,15 @@ class GQAAttention(Mixer):
             self._tc_bq[page_size] = ops.attention_tc_tile_queries(self.nq, self.nkv, self.hd, page_size)
         return self._tc_bq[page_size]
 
+    def mma_tile_queries(self) -> int:
+        """Queries per tile of the tensor-core kernel that keeps float32 softmax weights (0: this layer's steps do not
+        run on it): bfloat16 layers with variations, key and value widths it takes."""
+        if self.dtype != torch.bfloat16 or not self.is_varied:
+            return 0
+        if self._mma_bq is None:
+            self._mma_bq = ops.attention_mma_tile_queries(self.nq, self.nkv, self.hd, self.vd)
+        return self._mma_bq
+
     def step_arrays_key(self):
         """Mixers with equal keys add the same arrays in `prepare_step`: the engine asks one of them."""
         return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, str(self.dtype), self.is_varied)
@@ -170,8 +182,9 @@ class GQAAttention(Mixer):
         run: the tensor-core kernel's where it takes the step, else the CUDA-core kernel's."""
         page_size = getattr(builder, "page_size", 0)
         tc_bq = self.tc_tile_queries(page_size) if page_size and not builder.pure_decode else 0
-        if tc_bq:
-            self._tiles(builder, tc_bq, heaviest_first=True)
+        mma_bq = self.mma_tile_queries() if not builder.pure_decode else 0
+        if tc_bq or mma_bq:
+            self._tiles(builder, tc_bq or mma_bq, heaviest_first=True)
         else:
             self._tiles(builder, self.bq)
 
@@ -273,6 +286,17 @@ class GQAAttention(Mixer):
                       self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q,
                       pairing=self.pairing, head_norm=self.head_norm, bias=bias, vd=self.vd)
         o = ws.buffer("attn_o", T, self.nq * self.vd, self.dtype)
+        mma_bq = 0 if ctx.pure_decode else self.mma_tile_queries()
+        if mma_bq and ctx.has_array(f"attention_tiles_bq{mma_bq}_seq"):
+            # portions of prompts in bfloat16: the products on the tensor cores, the weights float32 (three terms)
+            tile_seq = ctx.array(f"attention_tiles_bq{mma_bq}_seq")
+            ops.attention_mma(o, q, cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, tile_seq,
+                              ctx.array(f"attention_tiles_bq{mma_bq}_q0"), tile_seq.numel(), self.nq, self.nkv, self.hd, self.vd,
+                              cache.page_size, self.window, float(self.spec.scale), softcap=self.softcap, sink=self.sink, gate=gate)
+            out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+            if self.o_bias is not None:
+                ops.add_bias(out, self.o_bias)
+            return out
         tile_seq = ctx.array(self.tiles_name + "_seq")
         tile_q0 = ctx.array(self.tiles_name + "_q0")
         # single decoded tokens: the keys in parts that are merged afterwards (the sink enters once, in the merge)

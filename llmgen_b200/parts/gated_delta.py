@@ -12,9 +12,9 @@ from .spec import VECTOR, GatedDeltaSpec, WeightDecl
 
 class GatedDelta(Mixer):
     """One packed projection [q | k | v | beta | decay's low rank | gate's low rank] -> the short convolution and silu
-    of q, k, v (float32 out) -> the two low-rank up-projections (the decay's into float32) -> the recurrence over each
-    sequence's new tokens, which also makes q and k unit vectors, exponentiates the decays and takes beta through its
-    sigmoid (csrc/recurrent.cu: `delta_scan`) -> RMSNorm of each head's output times sigmoid(gate), one kernel ->
+    of q, k, v (float32 out) -> the two low-rank up-projections (the decay's into float32) -> a pass over the tokens that
+    makes q and k unit vectors, exponentiates the decays and takes beta through its sigmoid, and the recurrence over each
+    sequence's new tokens (csrc/recurrent.cu: `delta_scan`, two launches) -> RMSNorm of each head's output times sigmoid(gate), one kernel ->
     output projection.
 
     State of a request, one float32 row of the cache manager's slots: [S (heads x key_dim x value_dim) | the
@@ -89,7 +89,8 @@ class GatedDelta(Mixer):
         gate = linear(packed[:, self.gate_off:], self.w_gate, ws.buffer("delta_gate", T, H * E, self.dtype))
         o = ws.buffer("delta_o", T, H * E, torch.float32)
         ops.delta_scan(o, qkv, packed[:, self.beta_off:self.decay_off], decay, self.dt_bias, self.a_log, cache.state, ctx.cu_q,
-                       ctx.state_slots, ctx.n_seqs, H, G, D, E, float(self.spec.unit_eps), float(D) ** -0.5)
+                       ctx.state_slots, ctx.n_seqs, H, G, D, E, float(self.spec.unit_eps), float(D) ** -0.5,
+                       beta_buf=ws.buffer("delta_beta", T, H + G, torch.float32))
         y = ws.buffer("delta_y", T, H * E, self.dtype)
         ops.gated_rmsnorm(y.view(T * H, E), o.view(T * H, E), gate.view(T * H, E), self.norm_gain, self.norm_eps)
         return linear_sliced(ws, "mixer_out", y, self.w_o, self.dtype)

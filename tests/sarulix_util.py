@@ -68,6 +68,14 @@ WIDE = config([
     delta(6, 2, 40, 72, 4, dense(48)),
     rglru(48, 2, 3, None),
 ], width=48, vocab=61, scale=1.0, eps=1e-6, loop=(0, 3, 3), logit_scale=1.5)
+# Key and value widths that the tensor-core attention of the bfloat16 engine takes (64 and 128, equal and not), beside a
+# recurrent layer; prompts of a few hundred tokens then cross several tiles of keys and of queries.
+TENSOR = config([
+    attention(4, 2, 64, 64, 0.125, dense(64), softcap=20.0, rot=(10000.0, 32)),
+    rglru(64, 2, 4, None),
+    attention(2, 1, 128, 64, 0.09, None, rot=(500.0, 128)),
+    attention(2, 2, 64, 128, 0.125, None, softcap=8.0),
+], width=64, vocab=97, scale=2.0, loop=(0, 2, 2))
 # One attention layer whose weights `plant_needle` rewrites so that one token's query finds one other token's key.
 NEEDLE = config([attention(2, 1, 64, 16, 0.25, dense(64), softcap=20.0, rot=(30.0, 8))], width=32, vocab=53, scale=2.0)
 NEEDLE_ID, PROBE_ID, FILLER_ID = 5, 9, 11

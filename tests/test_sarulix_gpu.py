@@ -34,6 +34,24 @@ def test_portions_of_any_size_and_single_tokens_give_the_whole_prompts_logits(dt
     assert drv.executor.cache.all_free()
 
 
+@pytest.mark.parametrize("eager", [True, False])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompts_that_cross_tiles_of_the_tensor_core_attention(dtype, eager):
+    """300 tokens whole, in portions whose tiles of 64 queries begin anywhere among the keys' tiles, and beside another
+    request; launched and replayed."""
+    cfg = su.TENSOR
+    model, tensors = su.build(cfg, seed=15, dtype=dtype)
+    ids, other = su.ids_for(cfg, 300, seed=5), su.ids_for(cfg, 90, seed=6)
+    want, want_other = su.plain_logits(cfg, tensors, ids), su.plain_logits(cfg, tensors, other)
+    drv = su.driver(model, dtype, pool_tokens=448, eager=eager)
+    su.assert_close(su.run_in_portions(drv, "a", ids, [300]), want, dtype)
+    su.assert_close(su.run_in_portions(drv, "a", ids, [130, 70, 1, 2, 97]), want, dtype)
+    got_a = [drv.step([("a", ids[:200], list(range(200)))])]
+    out = drv.step([("a", ids[200:], list(range(100))), ("b", other, list(range(90)))], end=["a", "b"])
+    su.assert_close(torch.cat([got_a[0], out[:100]]), want, dtype)
+    su.assert_close(out[100:], want_other, dtype)
+
+
 def test_the_logits_do_not_depend_on_the_cut_beyond_rounding():
     """float32: token by token, in twos and whole agree far inside the tolerance against the plain model."""
     cfg = su.WIDE

@@ -142,7 +142,8 @@ def test_delta_scan_carries_its_state_between_calls(H, G, D, E, dtype):
         cat = lambda xs: torch.cat([x[a:b] for x, (a, b) in zip(xs, cut)]).to(DEV)
         qkv, beta, decay = cat(qkvs), cat(betas), cat(decays).contiguous()
         out = torch.full((qkv.shape[0], H * E), float("nan"), device=DEV)
-        ops.delta_scan(out, qkv[:, 4:], beta[:, 1:1 + H], decay, dt_bias.to(DEV), a_log.to(DEV), state, cu, sl, 4, H, G, D, E, 1e-6, D ** -0.5)
+        ops.delta_scan(out, qkv[:, 4:], beta[:, 1:1 + H], decay, dt_bias.to(DEV), a_log.to(DEV), state, cu, sl, 4, H, G, D, E, 1e-6, D ** -0.5,
+                       beta_buf=torch.empty(qkv.shape[0], H + G, device=DEV))
         at = 0
         for i, m in enumerate(lens):
             outs[i].append(out[at:at + m].cpu())
@@ -162,10 +163,12 @@ def test_delta_scan_carries_its_state_between_calls(H, G, D, E, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,E,softcap,gate", [(4, 2, 16, 24, 15.0, True), (3, 3, 8, 8, 0.0, False), (8, 1, 32, 16, 5.0, True),
-                                                  (2, 1, 64, 128, 0.0, True)])
+                                                  (2, 1, 64, 128, 0.0, True), (4, 2, 128, 128, 20.0, True), (2, 2, 64, 64, 6.0, False),
+                                                  (3, 1, 128, 64, 0.0, True)])
 def test_attention_with_a_sink_a_bound_a_gate_and_values_of_their_own_width(H, G, D, E, softcap, gate, dtype):
     """Two sequences, the second with keys of an earlier step in shuffled pages; biases added by the preparation kernel;
-    the same rows through one launch and through key parts that are merged afterwards."""
+    the same rows through one launch, through key parts that are merged afterwards and, in bfloat16 at the widths it
+    takes, through the tensor-core kernel with float32 weights."""
     from llmgen_b200.kernels import ops
     page, scale = 16, 0.3
     lens, starts = [21, 9], [0, 40]
@@ -206,6 +209,15 @@ def test_attention_with_a_sink_a_bound_a_gate_and_values_of_their_own_width(H, G
         scratch = torch.empty(ops.attention_scratch_floats(30, H, E, parts), device=DEV) if parts > 1 else None
         ops.paged_attention(out, q, q.stride(0), kc, vc, tables.view(-1), 4, ctx, cu, tile_seq, tile_q0, len(tiles), 30, H, G, D, page, 0,
                             scale, parts, 0, scratch, vd=E, softcap=softcap, sink=True, gate=g)
+        results.append(out.float().cpu())
+    mma_bq = ops.attention_mma_tile_queries(H, G, D, E) if dtype == "bfloat16" else 0
+    assert (mma_bq > 0) == (dtype == "bfloat16" and D in (64, 128) and E in (64, 128))
+    if mma_bq:
+        mt = [(s, q0) for s in range(2) for q0 in range(0, lens[s], mma_bq)] + [(-1, 0)]
+        out = torch.full((30, H * E), float("nan"), device=DEV, dtype=dt)
+        ops.attention_mma(out, q, kc, vc, tables.view(-1), 4, ctx, cu, torch.tensor([t[0] for t in mt], dtype=torch.int32, device=DEV),
+                          torch.tensor([t[1] for t in mt], dtype=torch.int32, device=DEV), len(mt), H, G, D, E, page, 0, scale,
+                          softcap=softcap, sink=True, gate=g)
         results.append(out.float().cpu())
     at = 0
     for s in range(2):
