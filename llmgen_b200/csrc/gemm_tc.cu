@@ -60,6 +60,14 @@ struct Smem {
 // the division as a reciprocal and a product: the exact one is a call with a slow path, which keeps the
 // compiler from overlapping the elements of a row (measured: 9 us against 2 us for the epilogue of a tile)
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// The gated epilogue's activation: 1 silu, 2 the tanh form of gelu, z / 2 (1 + tanh(u)) = z sigmoid(2u) with
+// u = sqrt(2 / pi) (z + 0.044715 z^3), so that it costs what silu costs.
+enum { GATE_SILU = 1, GATE_GELU_TANH = 2 };
+__device__ __forceinline__ float gate_act(int act, float g) {
+    if (act == GATE_GELU_TANH) return __fdividef(g, 1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+    return silu(g);
+}
+int g_gate_act = GATE_SILU;      // of the launch being made (set by the entry point, passed to the kernel)
 
 
 // Persistent: block b computes tiles b, b + gridDim.x, ... (tile t = (t % m_tiles) rows, (t / m_tiles)
@@ -83,7 +91,7 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int store_by_tma, int splits,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag,
-               const int* __restrict__ tile_group) {
+               const int* __restrict__ tile_group, int act) {
     static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
     using L = Smem<BN, STAGES, MB, PAIR, KS>;
     constexpr int ROWS = (PAIR ? 2 : MB) * BM;                     // rows of a tile
@@ -326,7 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if constexpr (GATED) {
                                 float o[16];
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) o[i] = silu(__uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
+                                for (int i = 0; i < 16; ++i) o[i] = gate_act(act, __uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
 #pragma unroll
                                 for (int q = 0; q < 2; ++q) {
                                     Vec16<bf16> v;
@@ -415,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int j0 = (n0 + c0) / 2;
                     float o[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = silu(__uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
+                    for (int i = 0; i < 16; ++i) o[i] = gate_act(act, __uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
                     TC* dst = C + (size_t)row * ldc + j0;
                     if (vec_ok && j0 + 16 <= n_out) {
                         if constexpr (sizeof(TC) == 2) {
@@ -565,12 +573,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
         const int pairs = tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch_clusters(kernel, dim3(2 * pairs), dim3(THREADS), L::TOTAL, s, pdl != 0,
                                                              dim3(2, 1, 1), ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K,
-                                                             ldc, error_flag, tile_group));
+                                                             ldc, error_flag, tile_group, g_gate_act));
     } else {
         const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM) * splits;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
                                                     pdl != 0, ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K, ldc,
-                                                    error_flag, tile_group));
+                                                    error_flag, tile_group, g_gate_act));
     }
     return LLMK_OK;
 }
@@ -703,7 +711,7 @@ LLMK_EXPORT void llmk_gemm_tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 LLMK_EXPORT void llmk_gemm_tc_set_store_by_tma(int on) { g_store_by_tma = on; }
 
 // out_dtype: storage of C (bfloat16, or float32 for logits).  gated != 0: W interleaves gate and up
-// rows in groups of 16 and C is [M, N / 2].  error_flag (device int, may be null) is raised if a
+// rows in groups of 16 and C is [M, N / 2] = act(gate) * up, act = silu (gated 1) or the tanh form of gelu (gated 2).  error_flag (device int, may be null) is raised if a
 // wait inside the kernel gave up.
 LLMK_EXPORT int llmk_gemm_tc(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
                              long long ldw, long long ldc, int gated, int out_dtype, int* error_flag, int pdl,
@@ -712,6 +720,8 @@ LLMK_EXPORT int llmk_gemm_tc(void* C, const void* A, const void* W, int M, int N
     if (!llmk_gemm_tc_usable(A, W, M, N, K, lda, ldw))
         LLMK_FAIL("gemm_tc: operands not usable (K=%d lda=%lld ldw=%lld must be multiples of 8, bases 16-byte aligned)", K, lda, ldw);
     if (gated && N % 32 != 0) LLMK_FAIL("gemm_tc: gated epilogue needs N=%d to be a multiple of 32", N);
+    if (gated != 0 && gated != GATE_SILU && gated != GATE_GELU_TANH) LLMK_FAIL("gemm_tc: unknown gated activation %d", gated);
+    g_gate_act = gated ? gated : GATE_SILU;
     if (ldc < (gated ? N / 2 : N)) LLMK_FAIL("gemm_tc: ldc=%lld too small", ldc);
     if (ceil_div(M, BM) > 65535) LLMK_FAIL("gemm_tc: M=%d too large", M);
     cudaStream_t s = (cudaStream_t)stream;

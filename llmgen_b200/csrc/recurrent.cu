@@ -419,13 +419,13 @@ LLMK_EXPORT int llmk_rglru(void* out, long long out_ld, float* a_buf, float* b_b
 // and q . k of every key head is left beside it.  With S' = diag(g) S the token's read-out is
 // o = S^T q = S'^T q + (q . k) d, so both dot products over the key channels run over S' in one pass and the update
 // S = S' + k d^T ends the token: one chain of dependent steps a token instead of two.
-// `delta_scan`, a block per (sequence, head, tile of DELTA_COLS value columns) of 4 * DELTA_COLS threads: a lane holds a
-// quarter of one column of S (a contiguous run of key channels), so the two dot products of a token over the key
-// channels end in two shuffles.  The tokens come in chunks of DELTA_CHUNK through shared memory, the next chunk copied
+// `delta_scan`, a block of four warps per (sequence, head, tile of value columns): SL lanes share one column of S, each
+// holding a contiguous run of DSL key channels, so the dot products of a token over the key channels end in log2(SL)
+// shuffles.  A token's time is its chain of dependent steps (there is one warp a scheduler), which is shortest with many
+// lanes a column: 16 for key widths from 33 (8 value columns a block, 128 blocks for 8 heads of 128 columns).  The tokens come in chunks of DELTA_CHUNK through shared memory, the next chunk copied
 // (cp.async) while the columns walk the present one token by token.
 constexpr int DELTA_CHUNK = 16;
-constexpr int DELTA_COLS = 32;
-constexpr int DELTA_THREADS = 4 * DELTA_COLS;
+constexpr int DELTA_THREADS = 128;
 
 template <typename T>
 __global__ void __launch_bounds__(256) delta_prep_kernel(float* __restrict__ qkv, long long qkv_ld, float* __restrict__ decay,
@@ -484,42 +484,51 @@ __device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// One chunk's rows into shared memory: q, k, 1 - g as [CHUNK][4 slices][DSL + 4] (the padding keeps the four slices'
-// 16-byte reads on different banks), v as [CHUNK][COLS], beta [CHUNK].
-template <int DSL>
+// One chunk's rows into shared memory: q, k, 1 - g as [CHUNK][SL slices][STRIDE] (the padding keeps the slices' 16-byte
+// reads on different banks), v as [CHUNK][COLS], then beta [CHUNK] and q . k [CHUNK].
+template <int DSL, int SL>
+struct DeltaShape {
+    static constexpr int STRIDE = DSL == 4 ? 12 : DSL + 4;
+    static constexpr int ROW = SL * STRIDE;
+    static constexpr int COLS = 4 * (32 / SL);
+    static constexpr int BUF = DELTA_CHUNK * (3 * ROW + COLS) + 2 * DELTA_CHUNK;
+};
+
+template <int DSL, int SL>
 __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* buf, int t_first, int nc, int h, int kvh, int e0) {
-    constexpr int ROW = 4 * (DSL + 4);
+    using Sh = DeltaShape<DSL, SL>;
+    constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE;
     float* qs = buf;
     float* ks = qs + DELTA_CHUNK * ROW;
     float* gs = ks + DELTA_CHUNK * ROW;
     float* vs = gs + DELTA_CHUNK * ROW;
-    float* bs = vs + DELTA_CHUNK * DELTA_COLS;
+    float* bs = vs + DELTA_CHUNK * COLS;
     const int D = p.D, E = p.E, GD = p.G * p.D;
     if (p.vec_ok) {
         const int vecs = D / 4;
         for (int idx = threadIdx.x; idx < nc * vecs; idx += DELTA_THREADS) {
             const int tt = idx / vecs, d = (idx % vecs) * 4;
             const size_t t = (size_t)(t_first + tt);
-            const int at = tt * ROW + (d / DSL) * (DSL + 4) + d % DSL;
+            const int at = tt * ROW + (d / DSL) * STRIDE + d % DSL;
             cp_async16(qs + at, p.qkv + t * p.qkv_ld + (size_t)kvh * D + d);
             cp_async16(ks + at, p.qkv + t * p.qkv_ld + GD + (size_t)kvh * D + d);
             cp_async16(gs + at, p.decay + t * ((size_t)p.H * D) + (size_t)h * D + d);
         }
-        for (int idx = threadIdx.x; idx < nc * (DELTA_COLS / 4); idx += DELTA_THREADS) {
-            const int tt = idx / (DELTA_COLS / 4), cc = (idx % (DELTA_COLS / 4)) * 4;
-            if (e0 + cc < E) cp_async16(vs + tt * DELTA_COLS + cc, p.qkv + (size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc);
+        for (int idx = threadIdx.x; idx < nc * (COLS / 4); idx += DELTA_THREADS) {
+            const int tt = idx / (COLS / 4), cc = (idx % (COLS / 4)) * 4;
+            if (e0 + cc < E) cp_async16(vs + tt * COLS + cc, p.qkv + (size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc);
         }
     } else {
         for (int idx = threadIdx.x; idx < nc * D; idx += DELTA_THREADS) {
             const int tt = idx / D, d = idx % D;
             const size_t t = (size_t)(t_first + tt);
-            const int at = tt * ROW + (d / DSL) * (DSL + 4) + d % DSL;
+            const int at = tt * ROW + (d / DSL) * STRIDE + d % DSL;
             qs[at] = p.qkv[t * p.qkv_ld + (size_t)kvh * D + d];
             ks[at] = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
             gs[at] = p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d];
         }
-        for (int idx = threadIdx.x; idx < nc * DELTA_COLS; idx += DELTA_THREADS) {
-            const int tt = idx / DELTA_COLS, cc = idx % DELTA_COLS;
+        for (int idx = threadIdx.x; idx < nc * COLS; idx += DELTA_THREADS) {
+            const int tt = idx / COLS, cc = idx % COLS;
             if (e0 + cc < E) vs[idx] = p.qkv[(size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc];
         }
     }
@@ -530,14 +539,14 @@ __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* bu
     }
 }
 
-template <int DSL>
+template <int DSL, int SL>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p) {
-    constexpr int ROW = 4 * (DSL + 4);
-    constexpr int BUF = DELTA_CHUNK * (3 * ROW + DELTA_COLS) + 2 * DELTA_CHUNK;
+    using Sh = DeltaShape<DSL, SL>;
+    constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE, BUF = Sh::BUF;
     extern __shared__ __align__(16) float sm[];
-    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * DELTA_COLS;
+    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int slice = lane & 3, col = warp * 8 + (lane >> 2);
+    const int slice = lane % SL, col = warp * (32 / SL) + lane / SL;
     const int e = e0 + col;
     const int D = p.D, E = p.E;
     const int kvh = h / (p.H / p.G);
@@ -556,25 +565,27 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p
         S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
     }
     __syncthreads();
-    delta_load_chunk<DSL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, kvh, e0);
+    delta_load_chunk<DSL, SL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, kvh, e0);
     int turn = 0;
     for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK, turn ^= 1) {
         const int nc = min(DELTA_CHUNK, n - c0);
         cp_async_wait_all();
         __syncthreads();      // this chunk has arrived, and the chunk before is consumed by every warp
         if (c0 + DELTA_CHUNK < n)
-            delta_load_chunk<DSL>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, kvh, e0);
+            delta_load_chunk<DSL, SL>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, kvh, e0);
         const float* buf = sm + turn * BUF;
         const float* vs = buf + 3 * DELTA_CHUNK * ROW;
-        const float* bs = vs + DELTA_CHUNK * DELTA_COLS;
+        const float* bs = vs + DELTA_CHUNK * COLS;
         for (int tt = 0; tt < nc; ++tt) {
-            const float4* qr = reinterpret_cast<const float4*>(buf + tt * ROW + slice * (DSL + 4));
-            const float4* kr = reinterpret_cast<const float4*>(buf + DELTA_CHUNK * ROW + tt * ROW + slice * (DSL + 4));
-            const float4* gr = reinterpret_cast<const float4*>(buf + 2 * DELTA_CHUNK * ROW + tt * ROW + slice * (DSL + 4));
+            const float4* qr = reinterpret_cast<const float4*>(buf + tt * ROW + slice * STRIDE);
+            const float4* kr = reinterpret_cast<const float4*>(buf + DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
+            const float4* gr = reinterpret_cast<const float4*>(buf + 2 * DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
+            float4 kk[DSL / 4];
             float ks4[4] = {0.f, 0.f, 0.f, 0.f}, qs4[4] = {0.f, 0.f, 0.f, 0.f};   // four sums in turn: short chains of dependent adds
 #pragma unroll
             for (int i = 0; i < DSL / 4; ++i) {
                 const float4 g4 = gr[i], k4 = kr[i], q4 = qr[i];
+                kk[i] = k4;
                 S[4 * i] = fmaf(-g4.x, S[4 * i], S[4 * i]);
                 S[4 * i + 1] = fmaf(-g4.y, S[4 * i + 1], S[4 * i + 1]);
                 S[4 * i + 2] = fmaf(-g4.z, S[4 * i + 2], S[4 * i + 2]);
@@ -590,19 +601,19 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p
             }
             float kS = (ks4[0] + ks4[1]) + (ks4[2] + ks4[3]);
             float qS = (qs4[0] + qs4[1]) + (qs4[2] + qs4[3]);
-            kS += __shfl_xor_sync(0xffffffffu, kS, 1);
-            qS += __shfl_xor_sync(0xffffffffu, qS, 1);
-            kS += __shfl_xor_sync(0xffffffffu, kS, 2);
-            qS += __shfl_xor_sync(0xffffffffu, qS, 2);
-            const float dlt = bs[tt] * (vs[tt * DELTA_COLS + col] - kS);
+#pragma unroll
+            for (int o = 1; o < SL; o <<= 1) {
+                kS += __shfl_xor_sync(0xffffffffu, kS, o);
+                qS += __shfl_xor_sync(0xffffffffu, qS, o);
+            }
+            const float dlt = bs[tt] * (vs[tt * COLS + col] - kS);
             const float o = fmaf(bs[DELTA_CHUNK + tt], dlt, qS);
 #pragma unroll
             for (int i = 0; i < DSL / 4; ++i) {
-                const float4 k4 = kr[i];
-                S[4 * i] = fmaf(k4.x, dlt, S[4 * i]);
-                S[4 * i + 1] = fmaf(k4.y, dlt, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(k4.z, dlt, S[4 * i + 2]);
-                S[4 * i + 3] = fmaf(k4.w, dlt, S[4 * i + 3]);
+                S[4 * i] = fmaf(kk[i].x, dlt, S[4 * i]);
+                S[4 * i + 1] = fmaf(kk[i].y, dlt, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(kk[i].z, dlt, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(kk[i].w, dlt, S[4 * i + 3]);
             }
             if (slice == 0 && e < E) p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = o;
         }
@@ -616,14 +627,16 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p
     }
 }
 
-template <int DSL>
-static cudaError_t launch_delta(const DeltaParams& p, dim3 grid, cudaStream_t s) {
-    const size_t smem = 2 * ((size_t)DELTA_CHUNK * (3 * 4 * (DSL + 4) + DELTA_COLS) + 2 * DELTA_CHUNK) * sizeof(float);
+template <int DSL, int SL>
+static cudaError_t launch_delta(const DeltaParams& p, int n_seqs, cudaStream_t s) {
+    using Sh = DeltaShape<DSL, SL>;
+    const size_t smem = 2 * (size_t)Sh::BUF * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DSL, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return llmk_launch(delta_scan_kernel<DSL>, grid, dim3(DELTA_THREADS), smem, s, true, p);
+    dim3 grid(n_seqs, p.H, ceil_div(p.E, Sh::COLS));
+    return llmk_launch(delta_scan_kernel<DSL, SL>, grid, dim3(DELTA_THREADS), smem, s, true, p);
 }
 
 // qkv float32 [n_tokens, >= 2 G D + H E] and decay float32 [n_tokens, H D] are rewritten in place by the preparation;
@@ -636,7 +649,7 @@ LLMK_EXPORT int llmk_delta_scan(float* out, float* qkv, long long qkv_ld, const 
     if (H <= 0 || G <= 0 || H % G != 0) LLMK_FAIL("delta_scan: %d heads are not a multiple of %d key heads", H, G);
     if (D <= 0 || D > 256 || E <= 0) LLMK_FAIL("delta_scan: key width %d (at most 256) or value width %d", D, E);
     if (!out || !qkv || !beta || !decay || !beta_buf || !dt_bias || !a_log || !state || !cu_q || !state_slots) LLMK_FAIL("delta_scan: bad arguments");
-    if (H > 65535 || ceil_div(E, DELTA_COLS) > 65535) LLMK_FAIL("delta_scan: grid too large");
+    if (H > 65535 || ceil_div(E, 8) > 65535) LLMK_FAIL("delta_scan: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == LLMK_F32)
@@ -654,11 +667,10 @@ LLMK_EXPORT int llmk_delta_scan(float* out, float* qkv, long long qkv_ld, const 
     p.H = H; p.G = G; p.D = D; p.E = E;
     // 16-byte copies: every row of q, k, v and of the decays begins on a 16-byte boundary
     p.vec_ok = (D % 4 == 0 && E % 4 == 0 && qkv_ld % 4 == 0 && host_aligned16(qkv) && host_aligned16(decay)) ? 1 : 0;
-    dim3 grid(n_seqs, H, ceil_div(E, DELTA_COLS));
-    if (D <= 32) e = launch_delta<8>(p, grid, s);
-    else if (D <= 64) e = launch_delta<16>(p, grid, s);
-    else if (D <= 128) e = launch_delta<32>(p, grid, s);
-    else e = launch_delta<64>(p, grid, s);
+    if (D <= 32) e = launch_delta<4, 8>(p, n_seqs, s);
+    else if (D <= 64) e = launch_delta<4, 16>(p, n_seqs, s);
+    else if (D <= 128) e = launch_delta<8, 16>(p, n_seqs, s);
+    else e = launch_delta<16, 16>(p, n_seqs, s);
     LLMK_CHECK_LAUNCH_RC("delta_scan", e);
     return LLMK_OK;
 }

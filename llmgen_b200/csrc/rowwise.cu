@@ -105,7 +105,7 @@ __device__ __forceinline__ float gelu_tanh(float z) {
 
 template <typename T>
 __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x, int n, int F, long long ld, int mode,
-                                float alpha, float limit, int splits, long long split_stride) {
+                                float alpha, float limit, int splits, long long split_stride, int group) {
     pdl_launch_dependents();
     pdl_wait();
     const long long total = (long long)n * F;
@@ -117,7 +117,9 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
             const float a = fmaxf(load_sum<T>(x, r * ld + f, splits, split_stride), 0.f);
             v = a * a;
         } else if (mode == ACT_GELU_TANH_GLU) {
-            v = gelu_tanh(load_sum<T>(x, r * ld + f, splits, split_stride)) * load_sum<T>(x, r * ld + F + f, splits, split_stride);
+            // gate and up alternate in groups of `group` columns (group = F: all gates, then all ups)
+            const size_t gc = r * ld + (size_t)(f / group) * 2 * group + f % group;
+            v = gelu_tanh(load_sum<T>(x, gc, splits, split_stride)) * load_sum<T>(x, gc + group, splits, split_stride);
         } else {
             const float g = fminf(load_sum<T>(x, r * ld + f, splits, split_stride), limit);
             const float u = fminf(fmaxf(load_sum<T>(x, r * ld + F + f, splits, split_stride), -limit), limit);
@@ -128,17 +130,19 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
 }
 
 LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long ld, int mode, float alpha, float limit,
-                              int splits, long long split_stride, int dtype, void* stream) {
+                              int splits, long long split_stride, int group, int dtype, void* stream) {
     if (n <= 0 || F <= 0) return LLMK_OK;
+    if (group <= 0) group = F;
+    if (F % group != 0) LLMK_FAIL("act_rows: groups of %d columns do not divide %d", group, F);
     if (mode != ACT_RELU2 && mode != ACT_CLAMPED_GLU && mode != ACT_GELU_TANH_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
     long long blocks = ((long long)n * F + 255) / 256;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == LLMK_F32)
-        e = llmk_launch(act_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride);
+        e = llmk_launch(act_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride, group);
     else if (dtype == LLMK_BF16)
-        e = llmk_launch(act_rows_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride);
+        e = llmk_launch(act_rows_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride, group);
     else
         LLMK_FAIL("act_rows: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("act_rows", e);

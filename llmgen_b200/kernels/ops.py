@@ -373,10 +373,14 @@ def sm_count(device=None) -> int:
     return _sm_counts[key]
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = True) -> None:
+GATED_ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = True,
+            activation: str = "silu") -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T on the tensor cores (tcgen05), bfloat16 operands, float32
     accumulation; `out` is bfloat16 or float32.  With `gated`, w interleaves gate and up rows in
-    groups of 16 and out[M, N/2] = silu(gate) * up.  `pdl`: launched as a programmatic dependent of the
+    groups of 16 and out[M, N/2] = act(gate) * up, act = `activation` ("silu" or "gelu_tanh").  `pdl`: launched as a programmatic dependent of the
     kernel before it, like every other kernel here (its set-up then runs under that kernel's tail; a
     2,048-token prompt took 4.85 ms without and 4.45 ms with it)."""
     lib = build.load("gemm_tc")
@@ -389,8 +393,8 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
         raise KernelError("gemm_tc: operands must be bfloat16")
     _check(lib, lib.llmk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
                                  c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(_row_stride(out)),
-                                 c_int(1 if gated else 0), c_int(dtype_code(out.dtype)), _ptr(tc_error_flag(a.device)),
-                                 c_int(1 if pdl else 0), _stream()))
+                                 c_int(GATED_ACTIVATIONS[activation] if gated else 0), c_int(dtype_code(out.dtype)),
+                                 _ptr(tc_error_flag(a.device)), c_int(1 if pdl else 0), _stream()))
 
 
 ROWS8_MAX_ROWS = 8           # what the kernel takes
@@ -731,11 +735,11 @@ def cast_rows(out: torch.Tensor, src: torch.Tensor) -> None:
     _check(lib, lib.llmk_cast_rows(_ptr(out), _ptr(src), c_longlong(src.numel()), c_int(dtype_code(out.dtype)), _stream()))
 
 
-def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: float = 0.0) -> None:
+def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: float = 0.0, group: int = 0) -> None:
     """out[n, F] = relu(x)^2 ("relu2", x [n, F]) or the clamped gated unit of x [n, 2F] ("clamped_glu": gate in
     the first F columns, up in the last): g' = min(g, limit), u' = clamp(u, -limit, limit),
-    out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up of x [n, 2F] ("gelu_tanh_glu").  `x` is an array or a
-    `Partials`."""
+    out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up of x [n, 2F] ("gelu_tanh_glu", where `group` > 0 says
+    that gate and up columns alternate in groups of that many).  `x` is an array or a `Partials`."""
     lib = build.load("rowwise")
     try:
         mode = ACTIVATIONS[activation]
@@ -749,7 +753,7 @@ def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: f
         if x.dtype != out.dtype:
             raise KernelError("act_rows: input and output share the storage dtype")
     _check(lib, lib.llmk_act_rows(_ptr(out), _ptr(src), c_int(n), c_int(F), c_longlong(ld), c_int(mode), c_float(alpha), c_float(limit),
-                                  c_int(splits), c_longlong(stride), c_int(dtype_code(out.dtype)), _stream()))
+                                  c_int(splits), c_longlong(stride), c_int(group), c_int(dtype_code(out.dtype)), _stream()))
 
 
 def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> None:

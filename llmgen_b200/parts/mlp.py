@@ -47,12 +47,12 @@ class GatedMLP(FeedForward):
         self.spec = spec
         self.dtype = dtype
         F = spec.intermediate_size
-        # the products' gated epilogues apply silu; another activation runs as a pass over the packed product
+        # the few-rows products' gated epilogues apply silu only; the tiled product's takes the tanh form of gelu too
         self.silu = spec.activation == "silu"
         # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
         w_gate = weights.device_tensor(spec.gate_proj, dtype, device, keep=False)
         w_up = weights.device_tensor(spec.up_proj, dtype, device, keep=False)
-        if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0 and self.silu:
+        if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0:
             self.group = GATE_UP_GROUP
             packed = interleave_gate_up(w_gate, w_up)
         else:
@@ -74,8 +74,12 @@ class GatedMLP(FeedForward):
         ws = ctx.workspace
         act = ws.buffer("ffn_act", T, F, self.dtype)
         if not self.silu:
-            gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
-            ops.act_rows(act, gate_up, "gelu_tanh_glu")
+            # prompts: the activation in the tiled product's epilogue; few rows: a pass over the packed product
+            if self.group == GATE_UP_GROUP and T > ops.SKINNY_BEST_ROWS and gated_product_usable(x, self.w_gate_up):
+                ops.gemm_tc(act, x, self.w_gate_up, gated=True, activation=self.spec.activation)
+            else:
+                gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
+                ops.act_rows(act, gate_up, "gelu_tanh_glu", group=self.group)
             return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
         cluster = min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) if gated and T <= ops.SKINNY_CLUSTER_MAX_ROWS else 1

@@ -280,3 +280,26 @@ def test_the_small_row_kernels(dtype):
     close(logits, want, 1e-6)
     ops.logit_cap(logits, 2.0, 1.0)
     close(logits, 2.0 * torch.tanh(want / 2.0), 1e-6)
+
+
+def test_gelu_in_the_tiled_product_s_gated_epilogue_and_over_grouped_columns():
+    """gate and up rows interleaved in groups of 16: the tensor-core product with gelu_tanh(gate) * up in its epilogue,
+    and the pass over the packed product that few rows take, against the plain function."""
+    from llmgen_b200.kernels import ops
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    M, K, F = 200, 64, 96
+    x = rnd((M, K), 1, 1.0, torch.bfloat16)
+    wg, wu = rnd((F, K), 2, 0.3, torch.bfloat16), rnd((F, K), 3, 0.3, torch.bfloat16)
+    want = plain.gelu_tanh(x.double() @ wg.double().t()) * (x.double() @ wu.double().t())
+    w = interleave_gate_up(wg, wu).contiguous().to(DEV)
+    out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(out, x.to(DEV), w, gated=True, activation="gelu_tanh")
+    close(out.float(), want, 1e-2)
+    silu = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(silu, x.to(DEV), w, gated=True)                 # the default stays silu
+    g = x.double() @ wg.double().t()
+    close(silu.float(), g / (1 + torch.exp(-g)) * (x.double() @ wu.double().t()), 1e-2)
+    packed = torch.empty(M, 2 * F, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(packed, x.to(DEV), w)
+    ops.act_rows(out, packed, "gelu_tanh_glu", group=16)
+    close(out.float(), want, 1e-2)
