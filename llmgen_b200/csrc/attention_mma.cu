@@ -10,7 +10,7 @@
 //   finish         the sink (one more term exp(0) in the denominator), the division, the output gate sigmoid(g)
 //
 // Block = 64 queries of one sequence x one query head, four warps of 16 rows; keys in tiles of 64 through shared
-// memory (16-byte copies out of the pages).  Semantics as in csrc/attention.cu (which takes float32, single tokens in
+// memory: 16-byte `cp.async` copies out of the pages into two buffers, the next tile on its way while this one is used.  Semantics as in csrc/attention.cu (which takes float32, single tokens in
 // parts, and every size this kernel refuses): query j of a portion sits at position ctx - q_len + j.
 // Taken: key width and value width 64 or 128 each.
 #include "common.cuh"
@@ -50,6 +50,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// tanh(x) = 1 - 2 / (1 + e^(2x)): an absolute error of a few 1e-7, which is what a score needs (it is an exponent)
+__device__ __forceinline__ float tanh_abs(float x) { return 1.0f - __fdividef(2.0f, 1.0f + exp2f(x * 2.8853900817779268f)); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -67,8 +74,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
     constexpr int QLD = HD + 8, VLD = VD + 8;      // rows 16 bytes longer: the eight rows of an ldmatrix fall on different banks
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][QLD]
-    bf16* Ks = Qs + BM * QLD;                           // [BN][QLD]
-    bf16* Vs = Ks + BN * QLD;                           // [BN][VLD]
+    bf16* Kbuf = Qs + BM * QLD;                         // 2 x [BN][QLD]
+    bf16* Vbuf = Kbuf + 2 * BN * QLD;                   // 2 x [BN][VLD]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tq = lane & 3;
     const int s = p.tile_seq[blockIdx.x];
@@ -111,22 +118,32 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
     const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
     constexpr float LOG2E = 1.4426950408889634f;
 
-    for (int t0 = k_beg; t0 < k_end; t0 += BN) {
-        __syncthreads();          // the tile before is consumed
-        for (int idx = threadIdx.x; idx < BN * (HD / 8 + VD / 8); idx += blockDim.x) {
-            const int key = idx / (HD / 8 + VD / 8), v = idx % (HD / 8 + VD / 8);
+    constexpr int VECS = HD / 8 + VD / 8;
+    auto load_tile = [&](int t0, int buf) {
+        bf16* Kd = Kbuf + buf * BN * QLD;
+        bf16* Vd = Vbuf + buf * BN * VLD;
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < BN * VECS; idx += WARPS * 32) {
+            const int key = idx / VECS, v = idx % VECS;
             const int kpos = t0 + key;
-            uint4 val = make_uint4(0, 0, 0, 0);
+            bf16* dst = v < HD / 8 ? Kd + key * QLD + v * 8 : Vd + key * VLD + (v - HD / 8) * 8;
             if (kpos < k_end) {
                 const int page = bt[kpos / p.page_size];
                 const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
-                val = v < HD / 8 ? *reinterpret_cast<const uint4*>(p.kcache + row * HD + v * 8)
-                                 : *reinterpret_cast<const uint4*>(p.vcache + row * VD + (v - HD / 8) * 8);
+                cp_async16(dst, v < HD / 8 ? p.kcache + row * HD + v * 8 : p.vcache + row * VD + (v - HD / 8) * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
-            if (v < HD / 8) *reinterpret_cast<uint4*>(Ks + key * QLD + v * 8) = val;
-            else *reinterpret_cast<uint4*>(Vs + key * VLD + (v - HD / 8) * 8) = val;
         }
-        __syncthreads();
+    };
+    load_tile(k_beg, 0);
+    int turn = 0;
+    for (int t0 = k_beg; t0 < k_end; t0 += BN, turn ^= 1) {
+        cp_async_wait_all();
+        __syncthreads();          // this tile has arrived, and the tile before is consumed by every warp
+        if (t0 + BN < k_end) load_tile(t0 + BN, turn ^ 1);
+        const bf16* Ks = Kbuf + turn * BN * QLD;
+        const bf16* Vs = Vbuf + turn * BN * VLD;
         // a warp whose rows all lie before this tile's first key has nothing to do in it (causal)
         if (first_pos + warp * 16 + 15 < t0) continue;
 
@@ -152,7 +169,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
                 const int r = e >> 1;
                 const int kpos = t0 + n * 8 + 2 * tq + (e & 1);
                 float v = sc[n][e] * p.scale;
-                if (p.softcap > 0.f) v = p.softcap * tanhf(v * inv_cap);
+                if (p.softcap > 0.f) v = p.softcap * tanh_abs(v * inv_cap);
                 const bool vis = kpos <= qpos[r] && kpos < k_end && (p.window <= 0 || kpos > qpos[r] - p.window);
                 v = vis ? v : -INFINITY;
                 sc[n][e] = v;
@@ -244,9 +261,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
 
 template <int HD, int VD>
 int launch(const Params& p, dim3 grid, cudaStream_t s) {
-    const size_t smem = ((size_t)(BM + BN) * (HD + 8) + (size_t)BN * (VD + 8)) * sizeof(bf16);
+    const size_t smem = ((size_t)(BM + 2 * BN) * (HD + 8) + (size_t)2 * BN * (VD + 8)) * sizeof(bf16);
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
+    if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LLMK_FAIL("attention_mma: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         configured = true;
