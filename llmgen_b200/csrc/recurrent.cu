@@ -576,7 +576,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p
         const float* buf = sm + turn * BUF;
         const float* vs = buf + 3 * DELTA_CHUNK * ROW;
         const float* bs = vs + DELTA_CHUNK * COLS;
-        for (int tt = 0; tt < nc; ++tt) {
+        auto token = [&](int tt) {
             const float4* qr = reinterpret_cast<const float4*>(buf + tt * ROW + slice * STRIDE);
             const float4* kr = reinterpret_cast<const float4*>(buf + DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
             const float4* gr = reinterpret_cast<const float4*>(buf + 2 * DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
@@ -616,6 +616,12 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(DeltaParams p
                 S[4 * i + 3] = fmaf(kk[i].w, dlt, S[4 * i + 3]);
             }
             if (slice == 0 && e < E) p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = o;
+        };
+        if (nc == DELTA_CHUNK) {      // a whole chunk: the addresses are constants, and a token's tail runs under the next one's head
+#pragma unroll
+            for (int tt = 0; tt < DELTA_CHUNK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nc; ++tt) token(tt);
         }
     }
     if (st) {
