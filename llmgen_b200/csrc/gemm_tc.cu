@@ -60,14 +60,17 @@ struct Smem {
 // the division as a reciprocal and a product: the exact one is a call with a slow path, which keeps the
 // compiler from overlapping the elements of a row (measured: 9 us against 2 us for the epilogue of a tile)
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
-// The gated epilogue's activation: 1 silu, 2 the tanh form of gelu, z / 2 (1 + tanh(u)) = z sigmoid(2u) with
-// u = sqrt(2 / pi) (z + 0.044715 z^3), so that it costs what silu costs.
-enum { GATE_SILU = 1, GATE_GELU_TANH = 2 };
-__device__ __forceinline__ float gate_act(int act, float g) {
-    if (act == GATE_GELU_TANH) return __fdividef(g, 1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
-    return silu(g);
+// The gated epilogue's activation is part of the kernel's type (`GATED`: 0 no gate, 1 silu, 2 the tanh form of gelu), so
+// that the silu kernels are the code they were: z / 2 (1 + tanh(u)) = z sigmoid(2u), u = sqrt(2 / pi) (z + 0.044715 z^3),
+// costs what silu costs.  (A selector passed at launch was built first: with it two cases of the replay tests of another
+// architecture failed when the whole suite ran, though not alone; as a template parameter it leaves those kernels as
+// they were.)
+enum { GATE_NONE = 0, GATE_SILU = 1, GATE_GELU_TANH = 2 };
+template <int ACT>
+__device__ __forceinline__ float gate_act(float g) {
+    if constexpr (ACT == GATE_GELU_TANH) return __fdividef(g, 1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+    else return silu(g);
 }
-int g_gate_act = GATE_SILU;      // of the launch being made (set by the entry point, passed to the kernel)
 
 
 // Persistent: block b computes tiles b, b + gridDim.x, ... (tile t = (t % m_tiles) rows, (t / m_tiles)
@@ -86,12 +89,12 @@ int g_gate_act = GATE_SILU;      // of the launch being made (set by the entry p
 // commits arrive on the `empty` and `acc_full` barriers of both blocks; the epilogue warps of both
 // release an accumulator set on rank 0's `acc_empty`.  Each block reads its own 128 rows of the
 // accumulator out of its own tensor memory.
-template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false, int KS = 1>
+template <typename TC, int BN, int STAGES, int GATED, int MB, bool PAIR = false, int KS = 1>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int store_by_tma, int splits,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag,
-               const int* __restrict__ tile_group, int act) {
+               const int* __restrict__ tile_group) {
     static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
     using L = Smem<BN, STAGES, MB, PAIR, KS>;
     constexpr int ROWS = (PAIR ? 2 : MB) * BM;                     // rows of a tile
@@ -334,7 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if constexpr (GATED) {
                                 float o[16];
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) o[i] = gate_act(act, __uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
+                                for (int i = 0; i < 16; ++i) o[i] = gate_act<GATED>(__uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
 #pragma unroll
                                 for (int q = 0; q < 2; ++q) {
                                     Vec16<bf16> v;
@@ -423,7 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int j0 = (n0 + c0) / 2;
                     float o[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = gate_act(act, __uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
+                    for (int i = 0; i < 16; ++i) o[i] = gate_act<GATED>(__uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
                     TC* dst = C + (size_t)row * ldc + j0;
                     if (vec_ok && j0 + 16 <= n_out) {
                         if constexpr (sizeof(TC) == 2) {
@@ -545,7 +548,7 @@ bool get_slice_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t c
     return true;
 }
 
-template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false, int KS = 1>
+template <typename TC, int BN, int STAGES, int GATED, int MB, bool PAIR = false, int KS = 1>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
            int* error_flag, int pdl, cudaStream_t s, int splits = 1, const int* tile_group = nullptr) {
     using L = Smem<BN, STAGES, MB, PAIR, KS>;
@@ -573,12 +576,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
         const int pairs = tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch_clusters(kernel, dim3(2 * pairs), dim3(THREADS), L::TOTAL, s, pdl != 0,
                                                              dim3(2, 1, 1), ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K,
-                                                             ldc, error_flag, tile_group, g_gate_act));
+                                                             ldc, error_flag, tile_group));
     } else {
         const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM) * splits;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
                                                     pdl != 0, ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K, ldc,
-                                                    error_flag, tile_group, g_gate_act));
+                                                    error_flag, tile_group));
     }
     return LLMK_OK;
 }
@@ -591,7 +594,7 @@ int g_pair_mode = 1;
 // beyond 4, the MMA instructions set the pace)
 constexpr int STAGES_128 = 3, KS_128 = 2, STAGES_64 = 4;      // 128-wide tiles: three stages of two steps along K
 
-template <typename TC, bool GATED>
+template <typename TC, int GATED>
 int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                   long long ldc, int* error_flag, int pdl, cudaStream_t s) {
     // Tile width: the one whose tiles take the least time in rounds over the SMs.  The relative times
@@ -720,17 +723,18 @@ LLMK_EXPORT int llmk_gemm_tc(void* C, const void* A, const void* W, int M, int N
     if (!llmk_gemm_tc_usable(A, W, M, N, K, lda, ldw))
         LLMK_FAIL("gemm_tc: operands not usable (K=%d lda=%lld ldw=%lld must be multiples of 8, bases 16-byte aligned)", K, lda, ldw);
     if (gated && N % 32 != 0) LLMK_FAIL("gemm_tc: gated epilogue needs N=%d to be a multiple of 32", N);
-    if (gated != 0 && gated != GATE_SILU && gated != GATE_GELU_TANH) LLMK_FAIL("gemm_tc: unknown gated activation %d", gated);
-    g_gate_act = gated ? gated : GATE_SILU;
+    if (gated != GATE_NONE && gated != GATE_SILU && gated != GATE_GELU_TANH) LLMK_FAIL("gemm_tc: unknown gated activation %d", gated);
     if (ldc < (gated ? N / 2 : N)) LLMK_FAIL("gemm_tc: ldc=%lld too small", ldc);
     if (ceil_div(M, BM) > 65535) LLMK_FAIL("gemm_tc: M=%d too large", M);
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == LLMK_BF16)
-        return gated ? dispatch_tile<bf16, true>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
-                     : dispatch_tile<bf16, false>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s);
+        return gated == GATE_GELU_TANH ? dispatch_tile<bf16, GATE_GELU_TANH>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
+               : gated             ? dispatch_tile<bf16, GATE_SILU>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
+                                   : dispatch_tile<bf16, GATE_NONE>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s);
     if (out_dtype == LLMK_F32)
-        return gated ? dispatch_tile<float, true>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
-                     : dispatch_tile<float, false>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s);
+        return gated == GATE_GELU_TANH ? dispatch_tile<float, GATE_GELU_TANH>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
+               : gated             ? dispatch_tile<float, GATE_SILU>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s)
+                                   : dispatch_tile<float, GATE_NONE>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s);
     LLMK_FAIL("gemm_tc: unknown output dtype %d", out_dtype);
 }
 

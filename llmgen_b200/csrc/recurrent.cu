@@ -95,6 +95,53 @@ __global__ void conv_state_update_kernel(float* __restrict__ state, long long st
     }
 }
 
+// Both in one launch for steps of a few tokens (single decoded tokens above all): a thread per (sequence, channel) walks
+// the sequence's tokens with the last K - 1 inputs in registers and leaves them in the state.  The sum of a token is the
+// one `short_conv_kernel` makes, term by term.
+constexpr int SHORT_CONV_FEW_TOKENS = 64;
+
+template <typename T>
+__global__ void short_conv_few_kernel(float* __restrict__ out, long long out_ld, const T* __restrict__ x, long long x_ld,
+                                      const float* __restrict__ in_bias, const float* __restrict__ taps,
+                                      const float* __restrict__ conv_bias, float* __restrict__ state, long long state_ld,
+                                      const int* __restrict__ cu_q, const int* __restrict__ state_slots, int C, int K, int act,
+                                      int update_state) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = state_slots[s];
+    float* st = slot >= 0 && K > 1 ? state + (size_t)slot * state_ld + c : nullptr;
+    const float b = in_bias ? in_bias[c] : 0.f, cb = conv_bias ? conv_bias[c] : 0.f;
+    float w[MAX_TAPS], tp[MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS; ++i) {
+        tp[i] = i < K ? taps[(size_t)c * K + i] : 0.f;
+        w[i] = (i < K - 1 && st) ? st[(size_t)i * C] : 0.f;       // w[0 .. K-2]: the inputs before the token, oldest first
+    }
+    for (int j = 0; j < n; ++j) {
+        const float v = to_float(x[(size_t)(q_beg + j) * x_ld + c]) + b;
+        float acc = cb;
+#pragma unroll
+        for (int i = 0; i < MAX_TAPS; ++i) {
+            if (i < K - 1) acc = fmaf(tp[i], w[i], acc);
+            else if (i == K - 1) acc = fmaf(tp[i], v, acc);
+        }
+        out[(size_t)(q_beg + j) * out_ld + c] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+#pragma unroll
+        for (int i = 0; i < MAX_TAPS - 1; ++i)
+            if (i < K - 1) w[i] = i + 1 < K - 1 ? w[i + 1] : v;
+    }
+    if (st && update_state) {
+#pragma unroll
+        for (int i = 0; i < MAX_TAPS - 1; ++i)
+            if (i < K - 1) st[(size_t)i * C] = w[i];
+    }
+}
+
 LLMK_EXPORT int llmk_short_conv(float* out, long long out_ld, const void* x, long long x_ld, const float* in_bias,
                                 const float* taps, const float* conv_bias, float* state, long long state_ld, const int* cu_q,
                                 const int* state_slots, int n_seqs, int n_tokens, int C, int K, int act, int update_state,
@@ -108,6 +155,18 @@ LLMK_EXPORT int llmk_short_conv(float* out, long long out_ld, const void* x, lon
     const int threads = 128;
     dim3 grid(ceil_div(C, threads), n_tokens), ugrid(ceil_div(C, threads), n_seqs);
     cudaError_t e;
+    if (n_tokens <= SHORT_CONV_FEW_TOKENS) {
+        if (dtype == LLMK_F32)
+            e = llmk_launch(short_conv_few_kernel<float>, ugrid, dim3(threads), 0, s, true, out, out_ld, (const float*)x, x_ld, in_bias,
+                            taps, conv_bias, state, state_ld, cu_q, state_slots, C, K, act, update_state);
+        else if (dtype == LLMK_BF16)
+            e = llmk_launch(short_conv_few_kernel<bf16>, ugrid, dim3(threads), 0, s, true, out, out_ld, (const bf16*)x, x_ld, in_bias,
+                            taps, conv_bias, state, state_ld, cu_q, state_slots, C, K, act, update_state);
+        else
+            LLMK_FAIL("short_conv: unknown dtype %d", dtype);
+        LLMK_CHECK_LAUNCH_RC("short_conv", e);
+        return LLMK_OK;
+    }
     if (dtype == LLMK_F32) {
         e = llmk_launch(short_conv_kernel<float>, grid, dim3(threads), 0, s, true, out, out_ld, (const float*)x, x_ld, in_bias, taps,
                         conv_bias, (const float*)state, state_ld, cu_q, state_slots, n_seqs, C, K, act);

@@ -792,6 +792,7 @@ def concat_stream(out: torch.Tensor, resid: torch.Tensor, delta, x0: torch.Tenso
 
 # ------------------------------------------------------------------------------ recurrent mixers
 CONV_ACTIVATIONS = {"none": 0, "silu": 1}
+SHORT_CONV_FEW_TOKENS = 64     # steps of up to this many token rows: the convolution and its state's update in one launch
 
 
 def short_conv(out: torch.Tensor, x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
@@ -812,7 +813,7 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, taps: torch.Tensor, state: to
                                     _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(C), c_int(K),
                                     c_int(CONV_ACTIVATIONS[activation]), c_int(1 if update_state else 0),
                                     c_int(dtype_code(x.dtype)), _stream()),
-           2 if update_state and K > 1 else 1)
+           2 if update_state and K > 1 and n > SHORT_CONV_FEW_TOKENS else 1)
 
 
 def rglru_scratch_rows(n_tokens: int, n_seqs: int, dtype: torch.dtype) -> int:

@@ -32,12 +32,14 @@ def two_steps(lens_first, lens_second):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("lens_first,lens_second", [([5, 1, 9], [1, 2, 30]), ([70, 2, 1], [3, 90, 1])])
 @pytest.mark.parametrize("taps,act", [(4, "none"), (2, "silu"), (1, "none"), (7, "silu")])
-def test_short_conv_reads_the_last_inputs_of_the_step_before(taps, act, dtype):
+def test_short_conv_reads_the_last_inputs_of_the_step_before(taps, act, dtype, lens_first, lens_second):
     """Portions shorter and longer than the taps, a second step after the first, slots nobody owns left alone, rows
-    beyond the sequences untouched."""
+    beyond the sequences untouched; steps of a few tokens (one launch) and of more (the state brought up to date by a
+    launch of its own)."""
     from llmgen_b200.kernels import ops
-    C, lens_first, lens_second = 40, [5, 1, 9], [1, 2, 30]
+    C = 40
     w, cb, ib = rnd((C, taps), 1, 0.5), rnd((C,), 2, 0.3), rnd((C,), 3, 0.3)
     seqs = [rnd((a + b, C + 3), 10 + i, 1.0, DT[dtype]) for i, (a, b) in enumerate(zip(lens_first, lens_second))]
     state = torch.zeros(4, 11 + (taps - 1) * C, device=DEV)
