@@ -71,13 +71,13 @@ WIDE = config([
 # Key and value widths that the tensor-core attention of the bfloat16 engine takes (64 and 128, equal and not), beside a
 # recurrent layer; prompts of a few hundred tokens then cross several tiles of keys and of queries.
 TENSOR = config([
-    attention(4, 2, 64, 64, 0.125, dense(64), softcap=20.0, rot=(10000.0, 32)),
+    attention(6, 3, 64, 64, 0.11, dense(64), softcap=25.0, rot=(10000.0, 32)),
     rglru(64, 2, 4, None),
     attention(2, 1, 128, 64, 0.09, None, rot=(500.0, 128)),
     attention(2, 2, 64, 128, 0.125, None, softcap=8.0),
 ], width=64, vocab=97, scale=2.0, loop=(0, 2, 2))
 # One attention layer whose weights `plant_needle` rewrites so that one token's query finds one other token's key.
-NEEDLE = config([attention(2, 1, 64, 16, 0.25, dense(64), softcap=20.0, rot=(30.0, 8))], width=32, vocab=53, scale=2.0)
+NEEDLE = config([attention(2, 1, 64, 16, 0.25, dense(64), softcap=24.0, rot=(30.0, 8))], width=32, vocab=53, scale=2.0)
 NEEDLE_ID, PROBE_ID, FILLER_ID = 5, 9, 11
 # States that keep (nearly) everything and nothing else to carry information: losing a state, or a token of it, shows
 # at every later position.
@@ -123,7 +123,7 @@ def plant_needle(cfg: dict, tensors: Dict[str, torch.Tensor]) -> None:
     same matrix rows, with no biases and equal per-head gains; the first norm's gain is exactly one, so the two rows
     differ by a factor that the per-head norm removes; the probe's first half is the needle's second half.  The gains of
     the rotated values are small, so the position decides little.  The score of that pair is then scale * dim * gain^2
-    (16, bounded to 13.3 by the softcap) against about 2 for random directions: the probe's output is the needle's value
+    (16, bounded to 14 by the softcap) against about 2 for random directions: the probe's output is the needle's value
     times exp(s) / (1 + sum exp(s)), and a key or value that is not the one written for the needle shows far beyond
     rounding."""
     m = cfg["layers"][0]["mixer"]
