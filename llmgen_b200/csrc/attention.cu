@@ -1,7 +1,8 @@
 // Causal grouped-query attention over the paged key/value cache, float32 arithmetic on the CUDA
 // cores, for float32 or bfloat16 storage: the attention of the true 32-bit path, and the general
 // kernel of the bfloat16 path for every shape (prompt portions, single decoded tokens and both
-// mixed in one batch, any group size, any head_dim that is a multiple of 8 up to 512, a window).
+// mixed in one batch, any group size, any head_dim up to 512 (16-byte reads of the cache where key and value widths are
+// multiples of 8, else value by value), a window).
 //
 // Semantics follow the reference's CPU attention (src/backend/cpu/attention.zig:64-118):
 // sequence s owns query rows [cu_q[s], cu_q[s+1]) and has ctx[s] keys after this step; query j
@@ -120,27 +121,43 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 
     constexpr int VN = Vec16<T>::N;
     const int vecs = hd / VN, vvecs = vd / VN;
+    const bool vec_rows = hd % VN == 0 && vd % VN == 0;      // 16-byte reads of the cache's rows; else value by value
     for (int t0 = k_beg; t0 < k_end; t0 += KT) {
         __syncthreads();  // previous tile consumed (and Qs written, first time)
-        for (int idx = threadIdx.x; idx < KT * (vecs + vvecs); idx += blockDim.x) {
-            const int key = idx / (vecs + vvecs), vec = idx % (vecs + vvecs);
-            const bool is_k = vec < vecs;
-            const int kpos = t0 + key;
-            float f[VN];
-            if (kpos < k_end) {
-                const int page = bt[kpos / p.page_size];
-                const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
-                Vec16<T> v;
-                v.raw = is_k ? *reinterpret_cast<const decltype(v.raw)*>(kc + row * hd + (size_t)vec * VN)
-                             : *reinterpret_cast<const decltype(v.raw)*>(vc + row * vd + (size_t)(vec - vecs) * VN);
-                v.unpack(f);
-            } else {
+        if (vec_rows) {
+            for (int idx = threadIdx.x; idx < KT * (vecs + vvecs); idx += blockDim.x) {
+                const int key = idx / (vecs + vvecs), vec = idx % (vecs + vvecs);
+                const bool is_k = vec < vecs;
+                const int kpos = t0 + key;
+                float f[VN];
+                if (kpos < k_end) {
+                    const int page = bt[kpos / p.page_size];
+                    const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
+                    Vec16<T> v;
+                    v.raw = is_k ? *reinterpret_cast<const decltype(v.raw)*>(kc + row * hd + (size_t)vec * VN)
+                                 : *reinterpret_cast<const decltype(v.raw)*>(vc + row * vd + (size_t)(vec - vecs) * VN);
+                    v.unpack(f);
+                } else {
 #pragma unroll
-                for (int i = 0; i < VN; ++i) f[i] = 0.f;
+                    for (int i = 0; i < VN; ++i) f[i] = 0.f;
+                }
+                float* dst = is_k ? Ks + key * (hd + 1) + vec * VN : Vs + key * vd + (vec - vecs) * VN;
+#pragma unroll
+                for (int i = 0; i < VN; ++i) dst[i] = f[i];
             }
-            float* dst = is_k ? Ks + key * (hd + 1) + vec * VN : Vs + key * vd + (vec - vecs) * VN;
-#pragma unroll
-            for (int i = 0; i < VN; ++i) dst[i] = f[i];
+        } else {
+            for (int idx = threadIdx.x; idx < KT * (hd + vd); idx += blockDim.x) {
+                const int key = idx / (hd + vd), d = idx % (hd + vd);
+                const int kpos = t0 + key;
+                float f = 0.f;
+                if (kpos < k_end) {
+                    const int page = bt[kpos / p.page_size];
+                    const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
+                    f = d < hd ? to_float(kc[row * hd + d]) : to_float(vc[row * vd + (d - hd)]);
+                }
+                if (d < hd) Ks[key * (hd + 1) + d] = f;
+                else Vs[key * vd + (d - hd)] = f;
+            }
         }
         __syncthreads();
         if (!valid[0] && !valid[1]) continue;
@@ -150,6 +167,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
             const float* kr = Ks + lane * (hd + 1);
             const float4* qa = reinterpret_cast<const float4*>(Qs + r_of[0] * hd);
             const float4* qb = reinterpret_cast<const float4*>(Qs + (valid[1] ? r_of[1] : r_of[0]) * hd);
+            if (hd % 4 != 0) {
+                const float* sa = Qs + r_of[0] * hd;
+                const float* sb = Qs + (valid[1] ? r_of[1] : r_of[0]) * hd;
+                for (int d = 0; d < hd; ++d) {
+                    sc[0] = fmaf(sa[d], kr[d], sc[0]);
+                    sc[1] = fmaf(sb[d], kr[d], sc[1]);
+                }
+            } else
             for (int d4 = 0; d4 < hd / 4; ++d4) {
                 const float4 a = qa[d4], b = qb[d4];
                 const float k0 = kr[4 * d4], k1 = kr[4 * d4 + 1], k2 = kr[4 * d4 + 2], k3 = kr[4 * d4 + 3];
@@ -313,9 +338,9 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
-    if (hd <= 0 || hd % 8 != 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be a multiple of 8, at most 512", hd);
+    if (hd <= 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be positive, at most 512", hd);
     if (vd <= 0) vd = hd;
-    if (vd % 8 != 0 || vd > 512) LLMK_FAIL("paged_attention: value width %d must be a multiple of 8, at most 512", vd);
+    if (vd > 512) LLMK_FAIL("paged_attention: value width %d must be at most 512", vd);
     if (softcap < 0.f) LLMK_FAIL("paged_attention: softcap %g", (double)softcap);
     if (page_size <= 0) LLMK_FAIL("paged_attention: page_size %d", page_size);
     if (num_parts < 1 || (num_parts > 1 && !scratch)) LLMK_FAIL("paged_attention: bad split (%d parts, scratch %p)", num_parts, scratch);

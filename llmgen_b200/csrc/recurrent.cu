@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(GATE_OUT) rglru_gates_kernel(float* __restrict
                                                                const T* __restrict__ Wi, const float* __restrict__ ba,
                                                                const float* __restrict__ bi, const float* __restrict__ lam,
                                                                int n_tokens, int C, int n, float decay_scale, int vec_ok) {
-    extern __shared__ float Us[];   // [TT][n]
+    extern __shared__ __align__(16) float Us[];   // [TT][n]
     const int b = blockIdx.y, t0 = blockIdx.z * TT;
     const int o = blockIdx.x * GATE_OUT + threadIdx.x;
     pdl_launch_dependents();
@@ -224,14 +224,22 @@ __global__ void __launch_bounds__(GATE_OUT) rglru_gates_kernel(float* __restrict
             float fa[VN], fi[VN];
             va.unpack(fa);
             vi.unpack(fi);
+            // u comes four values a read (the rows of Us begin on 16-byte boundaries: n is a multiple of four here)
 #pragma unroll
-            for (int j = 0; j < VN; ++j)
+            for (int tt = 0; tt < TT; ++tt) {
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt) {
-                    const float uv = Us[tt * n + k + j];
-                    accA[tt] = fmaf(fa[j], uv, accA[tt]);
-                    accI[tt] = fmaf(fi[j], uv, accI[tt]);
+                for (int j4 = 0; j4 < VN / 4; ++j4) {
+                    const float4 u4 = *reinterpret_cast<const float4*>(Us + tt * n + k + 4 * j4);
+                    accA[tt] = fmaf(fa[4 * j4], u4.x, accA[tt]);
+                    accA[tt] = fmaf(fa[4 * j4 + 1], u4.y, accA[tt]);
+                    accA[tt] = fmaf(fa[4 * j4 + 2], u4.z, accA[tt]);
+                    accA[tt] = fmaf(fa[4 * j4 + 3], u4.w, accA[tt]);
+                    accI[tt] = fmaf(fi[4 * j4], u4.x, accI[tt]);
+                    accI[tt] = fmaf(fi[4 * j4 + 1], u4.y, accI[tt]);
+                    accI[tt] = fmaf(fi[4 * j4 + 2], u4.z, accI[tt]);
+                    accI[tt] = fmaf(fi[4 * j4 + 3], u4.w, accI[tt]);
                 }
+            }
         }
     }
     for (; k < n; ++k) {
@@ -331,7 +339,22 @@ __global__ void rglru_segment_local_kernel(const float* __restrict__ a, float* _
     // rounded at every token, always the same way where the decays hardly change, and the carried state takes a
     // segment's error 1 / (1 - product) times
     float S = 0.f, L = 0.f;
-    for (int t = t0; t < t1; ++t) {
+    int t = t0;
+    for (; t + 8 <= t1; t += 8) {          // eight tokens' loads in flight at a time
+        float cv[8], bv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            cv[i] = a[(size_t)(t + i) * C + c];
+            bv[i] = bx[(size_t)(t + i) * C + c];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            S = fmaf(-cv[i], S, S) + bv[i];
+            L += log1pf(-cv[i]);
+            bx[(size_t)(t + i) * C + c] = S;
+        }
+    }
+    for (; t < t1; ++t) {
         const float cv = a[(size_t)t * C + c];
         S = fmaf(-cv, S, S) + bx[(size_t)t * C + c];
         L += log1pf(-cv);
@@ -379,7 +402,23 @@ __global__ void rglru_segment_finish_kernel(T* __restrict__ out, long long out_l
     const float in = seg_in[(size_t)j * C + c];
     const float yb = y_bias ? y_bias[c] : 0.f;
     float L = 0.f;
-    for (int t = t0; t < t1; ++t) {
+    int t = t0;
+    for (; t + 8 <= t1; t += 8) {
+        float cv[8], lv[8], yv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            cv[i] = a[(size_t)(t + i) * C + c];
+            lv[i] = local[(size_t)(t + i) * C + c];
+            yv[i] = to_float(y[(size_t)(t + i) * y_ld + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            L += log1pf(-cv[i]);
+            const float S = fmaf(expf(L), in, lv[i]);
+            out[(size_t)(t + i) * out_ld + c] = from_float<T>(S * gelu_tanhf_(yv[i] + yb));
+        }
+    }
+    for (; t < t1; ++t) {
         L += log1pf(-a[(size_t)t * C + c]);
         const float S = fmaf(expf(L), in, local[(size_t)t * C + c]);
         out[(size_t)t * out_ld + c] = from_float<T>(S * gelu_tanhf_(to_float(y[(size_t)t * y_ld + c]) + yb));

@@ -100,16 +100,16 @@ class GQAAttention(Mixer):
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
         if spec.num_heads % spec.num_kv_heads != 0:
             raise ValueError(f"attention: {spec.num_heads} heads are not a multiple of {spec.num_kv_heads} kv heads")
-        if spec.head_dim % 8 != 0 or spec.head_dim > 512:
-            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 8, at most 512")
+        if spec.head_dim % 2 != 0 or spec.head_dim > 512:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be even, at most 512")
         for n in (spec.q_norm, spec.k_norm):
             if n is not None and (n.kind not in ops.HEAD_NORMS or n.dim != spec.head_dim):
                 raise ValueError(f"attention: per-head norms must run over head_dim and be one of {sorted(ops.HEAD_NORMS)}")
         self.spec = spec
         self.dtype = dtype
         self.nq, self.nkv, self.hd, self.vd = spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim
-        if self.vd % 8 != 0 or self.vd > 512:
-            raise ValueError(f"attention: the values' width {self.vd} must be a multiple of 8, at most 512")
+        if self.vd > 512:
+            raise ValueError(f"attention: the values' width {self.vd} must be at most 512")
         self.is_varied = self.varied(spec)
         # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
         names = [spec.q_proj, spec.k_proj, spec.v_proj] + ([spec.gate_proj] if spec.gate_proj else [])

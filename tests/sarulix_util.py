@@ -53,12 +53,13 @@ MIXED = config([
 ], loop=(1, 3, 2), logit_scale=0.7)
 # Sizes that are multiples of little (the products fall back from the TMA-fed kernels, vector loads to scalar ones),
 # values that a usual model makes equal or one: one block, one head, as many key heads as heads, the whole head
-# rotated, no bound on the scores, no loop, the logits as they are, two taps and five.
+# rotated, no bound on the scores, no loop, the logits as they are, two taps and five, key and value widths of the
+# attention that are no multiples of 8 or of 4.
 ODD = config([
-    attention(3, 3, 8, 8, 0.4, None, rot=(77.0, 8)),
+    attention(3, 3, 12, 20, 0.4, None, rot=(77.0, 12)),
     rglru(36, 1, 2, dense(30)),
     delta(1, 1, 10, 6, 5, None, decay_rank=3, gate_rank=5),
-    attention(2, 1, 24, 16, 0.2, dense(20), softcap=4.0),
+    attention(2, 1, 10, 6, 0.2, dense(20), softcap=4.0),
 ], width=36, vocab=50, scale=0.5, eps=1e-4)
 # A loop from the first layer on, three times; eight query heads on one key head; more value columns than one block of
 # the delta rule's kernel takes (72 > 64), a key width that is no multiple of four times anything (40).

@@ -1037,7 +1037,7 @@ def test_attention_refuses_what_it_cannot_do(ops):
     z = torch.zeros(1, 20, device="cuda")
     zi = torch.zeros(4, dtype=torch.int32, device="cuda")
     with pytest.raises(ops.KernelError, match="head_dim"):
-        ops.paged_attention(z, z, 20, z, z, zi, 1, zi, zi, zi, zi, 1, 1, 1, 1, 20, 16, 0, 1.0)
+        ops.paged_attention(z, z, 20, z, z, zi, 1, zi, zi, zi, zi, 1, 1, 1, 1, 520, 16, 0, 1.0)
     with pytest.raises(ops.KernelError, match="multiple"):
         ops.paged_attention(z, z, 48, z, z, zi, 1, zi, zi, zi, zi, 1, 1, 3, 2, 16, 16, 0, 1.0)
 
